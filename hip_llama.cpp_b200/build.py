@@ -2,11 +2,13 @@
 
     python hip_llama.cpp_b200/build.py            # everything that is out of date
     python hip_llama.cpp_b200/build.py --force
+    python hip_llama.cpp_b200/build.py --programs trace_run     # the libraries and the named programs only
 
 Outputs (git-ignored, but they travel to the GPU box with the snapshot):
     hip_llama.cpp_b200/lib/libtha_b200.so    CUDA kernels + the extern "C" boundary (include/tha_b200.h)
     hip_llama.cpp_b200/lib/libthablas.so     C++ host layer with the reference's names (include/thaBLAS.hpp ...)
     build/apps/llama                         the batching driver (reference: Makefile:9-26 -> build/apps/llama)
+    build/apps/trace_run                     replays scheduler steps through the layer-program serving path
     build/tests/*                            C++ API tests
 """
 from __future__ import annotations
@@ -96,8 +98,9 @@ def build_host(force: bool = False) -> str | None:
     return so
 
 
-def build_programs(force: bool = False) -> list[str]:
-    """The driver app and the C++ API tests (sources under apps/ and tests/cpp/)."""
+def build_programs(force: bool = False, only: list[str] | None = None) -> list[str]:
+    """The driver app, the trace runner and the C++ API tests (sources under apps/ and tests/cpp/); `only` names the
+    programs to build (default: all)."""
     out = []
     targets = []
     apps = os.path.join(PKG, "apps")
@@ -110,6 +113,8 @@ def build_programs(force: bool = False) -> list[str]:
         for f in sorted(os.listdir(tcpp)):
             if f.endswith(".cpp"):
                 targets.append((os.path.join(tcpp, f), os.path.join(ROOT, "build", "tests", f[:-4])))
+    if only is not None:
+        targets = [t for t in targets if os.path.basename(t[1]) in only]
     for src, exe in targets:
         os.makedirs(os.path.dirname(exe), exist_ok=True)
         if force or _newer(exe, [src] + headers() + [os.path.join(LIB, "libthablas.so")]):
@@ -119,12 +124,15 @@ def build_programs(force: bool = False) -> list[str]:
     return out
 
 
-def build_all(force: bool = False) -> dict:
+def build_all(force: bool = False, programs: list[str] | None = None) -> dict:
     res = {"cabi": build_cabi(force)}
     res["host"] = build_host(force)
-    res["programs"] = build_programs(force) if res["host"] else []
+    res["programs"] = build_programs(force, programs) if res["host"] else []
     return res
 
 
 if __name__ == "__main__":
-    print(build_all(force="--force" in sys.argv))
+    only = None
+    if "--programs" in sys.argv:   # python build.py --programs trace_run,llama: the libraries and these programs only
+        only = sys.argv[sys.argv.index("--programs") + 1].split(",")
+    print(build_all(force="--force" in sys.argv, programs=only))

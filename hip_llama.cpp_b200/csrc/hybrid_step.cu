@@ -1,0 +1,230 @@
+// tha_hyb_step: one scheduler step of a layer-program model (include/tha_hybrid.h) over ragged rows.
+// The layer loop walks the model's layer descriptions and issues the mechanisms of hybrid_ops.cu; every matrix that
+// reads a layer's normed input is one stacked product, its columns are handed to the mixers, the router and the shared
+// expert by offset.  Scratch is one slab owned by the library, carved per step.
+#include <cuda_bf16.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "hybrid_ops.cuh"
+#include "tha_hybrid.h"
+
+namespace tha {
+
+template <typename T>
+__global__ void hyb_embed_kernel(float* __restrict__ x, const T* __restrict__ embed, const int* __restrict__ token, int width) {
+  const int r = blockIdx.x;
+  const T* e = embed + (size_t)token[r] * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) x[(size_t)r * width + i] = hyb_load(e + i);
+}
+
+// x += mixer + feed-forward.  Two-sided mixers: each side's projection is normed over the width with its own weight,
+// the mixer is half their sum.  Feed-forward: the chosen experts' outputs by router weight (found through `inv` in the
+// expert-sorted buffer), plus the shared expert.
+__global__ void hyb_finish_kernel(float* __restrict__ x, int width, float eps, const float* __restrict__ left, const float* __restrict__ right,
+                                  const float* __restrict__ w_left, const float* __restrict__ w_right, int top,
+                                  const float* __restrict__ weight, const int* __restrict__ inv, const float* __restrict__ down,
+                                  const float* __restrict__ shared_down, float* __restrict__ tap) {
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  const float* l = left + (size_t)r * width;
+  float il = 1.f, ir = 0.f;
+  if (right) {
+    const float* rr = right + (size_t)r * width;
+    float sl = 0.f, sr = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) { sl = fmaf(l[i], l[i], sl); sr = fmaf(rr[i], rr[i], sr); }
+    sl = block_sum(sl, red);
+    sr = block_sum(sr, red);
+    il = 1.0f / sqrtf(sl / (float)width + eps);
+    ir = 1.0f / sqrtf(sr / (float)width + eps);
+  }
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float y = right ? 0.5f * (l[i] * il * w_left[i] + right[(size_t)r * width + i] * ir * w_right[i]) : l[i];
+    float f = 0.f;
+    for (int j = 0; j < top; j++) f = fmaf(weight[(size_t)r * top + j], down[(size_t)inv[(size_t)r * top + j] * width + i], f);
+    if (shared_down) f += shared_down[(size_t)r * width + i];
+    const float v = x[(size_t)r * width + i] + (y + f);
+    x[(size_t)r * width + i] = v;
+    if (tap) tap[(size_t)r * width + i] = v;
+  }
+}
+
+__global__ void hyb_softcap_kernel(float* __restrict__ z, size_t n, float cap) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) z[i] = cap * tanhf(z[i] / cap);
+}
+
+// ---- scratch -------------------------------------------------------------------------------------------------------
+struct HybScratch { char* base = nullptr; size_t cap = 0; std::mutex mu; };
+static HybScratch g_scratch[64];
+
+struct Carver {
+  char* base; size_t at = 0;
+  template <typename T> T* take(size_t n) {
+    at = (at + 255) & ~(size_t)255;
+    T* p = base ? reinterpret_cast<T*>(base + at) : nullptr;
+    at += n * sizeof(T);
+    return p;
+  }
+};
+
+struct StepBuffers {
+  float *x, *proj, *q, *left, *right, *conv, *dt_raw, *gate_raw, *gu, *down, *sdown, *weight;
+  void *h, *abuf, *mbuf, *y, *sy, *hn;
+  int *expert_id, *group_off, *sorted_row, *inv;
+  float* cos_t[16]; float* sin_t[16];
+};
+
+static size_t carve(const tha_hyb_model_t* m, int R, int n_want, char* base, StepBuffers* b) {
+  Carver c{base};
+  const size_t W = m->width, es = m->dtype == THA_DT_BF16 ? 2 : 4;
+  size_t n_in = 0, qd = 0, av = 0, mv = 0, cc = 0, dd = 0, dg = 0, gu = 0, ff = 0, sff = 0, top = 0, ne = 0;
+  for (int i = 0; i < m->n_layers; i++) {
+    const tha_hyb_layer_t& L = m->layers[i];
+    n_in = max(n_in, (size_t)L.n_in);
+    if (L.mixer == THA_MIX_PARALLEL) {
+      qd = max(qd, (size_t)L.attn.heads * L.attn.dim);
+      av = max(av, (size_t)L.attn.heads * L.attn.vdim);
+      mv = max(mv, (size_t)L.mem.heads * L.mem.vdim);
+    } else {
+      cc = max(cc, (size_t)2 * L.delta.kv_heads * L.delta.dim + (size_t)L.delta.heads * L.delta.vdim);
+      dd = max(dd, (size_t)L.delta.heads * L.delta.dim);
+      dg = max(dg, (size_t)L.delta.heads * L.delta.vdim);
+      mv = max(mv, (size_t)L.delta.heads * L.delta.vdim);
+    }
+    if (L.has_ff) {
+      top = max(top, (size_t)L.moe.top);
+      ne = max(ne, (size_t)L.moe.experts);
+      gu = max(gu, (size_t)L.moe.top * 2 * L.moe.ff);
+      ff = max(ff, (size_t)L.moe.top * L.moe.ff);
+      sff = max(sff, (size_t)L.moe.shared_ff);
+    }
+  }
+  b->x = c.take<float>(R * W);
+  b->h = c.take<char>(R * W * es);
+  b->proj = c.take<float>(R * n_in);
+  b->q = c.take<float>(R * qd);
+  b->abuf = c.take<char>(R * av * es);
+  b->mbuf = c.take<char>(R * mv * es);
+  b->left = c.take<float>(R * W);
+  b->right = c.take<float>(R * W);
+  b->conv = c.take<float>(R * cc);
+  b->dt_raw = c.take<float>(R * dd);
+  b->gate_raw = c.take<float>(R * dg);
+  b->gu = c.take<float>(R * gu);
+  b->y = c.take<char>(R * ff * es);
+  b->down = c.take<float>(R * top * W);
+  b->sy = c.take<char>(R * sff * es);
+  b->sdown = c.take<float>(R * W);
+  b->weight = c.take<float>(R * top);
+  b->expert_id = c.take<int>(R * top);
+  b->sorted_row = c.take<int>(R * top);
+  b->inv = c.take<int>(R * top);
+  b->group_off = c.take<int>(2 * (ne + 1));
+  b->hn = c.take<char>((size_t)n_want * W * es);
+  for (int i = 0; i < m->n_rot && i < 16; i++) {
+    b->cos_t[i] = c.take<float>((size_t)R * (m->rot[i].dims / 2));
+    b->sin_t[i] = c.take<float>((size_t)R * (m->rot[i].dims / 2));
+  }
+  return c.at + 256;
+}
+
+}  // namespace tha
+
+using namespace tha;
+typedef __nv_bfloat16 bf16;
+
+#define HYB_OK(expr)                         \
+  do {                                       \
+    const int _s = (expr);                   \
+    if (_s != THA_STATUS_SUCCESS) return _s; \
+  } while (0)
+
+extern "C" int tha_hyb_step(void* stream, const tha_hyb_model_t* m, const tha_rows_t* rows, const tha_kv_t* kv,
+                            const tha_state_store_t* st, int n_want, const int* want_rows, float* logits, float* taps) {
+  if (!m || !rows || !kv || !st || m->n_rot > 16) return THA_STATUS_INVALID_ARG;
+  const int R = rows->n_rows;
+  if (R < 1) return THA_STATUS_SUCCESS;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int dt = m->dtype, W = m->width;
+  int dev = 0;
+  THA_CUDA_OK(cudaGetDevice(&dev));
+  HybScratch& sc = g_scratch[dev & 63];
+  std::lock_guard<std::mutex> lock(sc.mu);
+  StepBuffers b;
+  const size_t need = carve(m, R, n_want, nullptr, &b);
+  if (need > sc.cap) {   // grow: nothing of an earlier step may still be using the old slab
+    THA_CUDA_OK(cudaDeviceSynchronize());
+    if (sc.base) THA_CUDA_OK(cudaFree(sc.base));
+    sc.base = nullptr; sc.cap = 0;
+    const size_t want = need + need / 2;
+    THA_CUDA_OK(cudaMalloc((void**)&sc.base, want));
+    sc.cap = want;
+  }
+  carve(m, R, n_want, sc.base, &b);
+
+  if (dt == THA_DT_BF16)
+    THA_CUDA_OK(launch(hyb_embed_kernel<bf16>, dim3(R), dim3(128), 0, s, false, b.x, (const bf16*)m->embed, rows->token, W));
+  else
+    THA_CUDA_OK(launch(hyb_embed_kernel<float>, dim3(R), dim3(128), 0, s, false, b.x, (const float*)m->embed, rows->token, W));
+  for (int i = 0; i < m->n_rot; i++) HYB_OK(tha_hyb_rotary_table(stream, &m->rot[i], rows->pos, R, b.cos_t[i], b.sin_t[i]));
+
+  for (int li = 0; li < m->n_layers; li++) {
+    const tha_hyb_layer_t& L = m->layers[li];
+    const long long ldp = L.n_in;
+    HYB_OK(tha_hyb_rmsnorm(stream, dt, b.h, b.x, L.norm1, 1.0f, m->eps, R, W, nullptr));
+    HYB_OK(tha_hyb_linear(stream, dt, b.proj, ldp, b.h, W, 0, nullptr, L.w_in, 0, R, L.n_in, W, nullptr, 0));
+    const float* right = nullptr;
+    if (L.mixer == THA_MIX_PARALLEL) {
+      const tha_attn_t& a = L.attn;
+      const int rd = a.rot >= 0 ? m->rot[a.rot].dims : 0;
+      HYB_OK(tha_hyb_attn_prepare(stream, &a, rows, kv, b.proj, ldp, a.rot >= 0 ? b.cos_t[a.rot] : nullptr,
+                                  a.rot >= 0 ? b.sin_t[a.rot] : nullptr, rd, b.q));
+      HYB_OK(tha_hyb_attn(stream, dt, &a, rows, kv, b.q, b.abuf));
+      HYB_OK(tha_hyb_linear(stream, dt, b.left, W, b.abuf, a.heads * a.vdim, 0, nullptr, a.w_o, 0, R, W, a.heads * a.vdim, nullptr, 0));
+      const tha_mem_t& mm = L.mem;
+      HYB_OK(tha_hyb_mem_scan(stream, dt, &mm, rows, st, b.proj, ldp, b.mbuf));
+      HYB_OK(tha_hyb_linear(stream, dt, b.right, W, b.mbuf, mm.heads * mm.vdim, 0, nullptr, mm.w_o, 0, R, W, mm.heads * mm.vdim, nullptr, 0));
+      right = b.right;
+    } else if (L.mixer == THA_MIX_DELTA) {
+      const tha_delta_t& d = L.delta;
+      const int C = 2 * d.kv_heads * d.dim + d.heads * d.vdim;
+      HYB_OK(tha_hyb_conv_silu(stream, rows, st, d.conv_state_off, b.proj, ldp, d.o_q, C, d.taps, d.conv, b.conv));
+      HYB_OK(tha_hyb_linear(stream, dt, b.dt_raw, d.heads * d.dim, b.proj + d.o_a1, ldp, 1, nullptr, d.w_a2, 0, R, d.heads * d.dim, d.rank_a, nullptr, 0));
+      HYB_OK(tha_hyb_linear(stream, dt, b.gate_raw, d.heads * d.vdim, b.proj + d.o_g1, ldp, 1, nullptr, d.w_g2, 0, R, d.heads * d.vdim, d.rank_g, nullptr, 0));
+      HYB_OK(tha_hyb_delta_scan(stream, dt, &d, rows, st, b.conv, b.proj, ldp, b.dt_raw, b.gate_raw, b.mbuf));
+      HYB_OK(tha_hyb_linear(stream, dt, b.left, W, b.mbuf, d.heads * d.vdim, 0, nullptr, d.w_o, 0, R, W, d.heads * d.vdim, nullptr, 0));
+    } else {
+      return THA_STATUS_NOT_SUPPORTED;
+    }
+    int top = 0;
+    const float* sdown = nullptr;
+    if (L.has_ff) {
+      const tha_moe_t& e = L.moe;
+      top = e.top;
+      HYB_OK(tha_hyb_moe_route(stream, &e, b.proj, ldp, R, b.expert_id, b.weight, b.group_off, b.sorted_row, b.inv));
+      HYB_OK(tha_hyb_linear(stream, dt, b.gu, 2 * e.ff, b.h, W, 0, b.sorted_row, e.w_gate_up, (long long)2 * e.ff * W, R * top, 2 * e.ff, W,
+                            b.group_off, e.experts));
+      HYB_OK(tha_hyb_glu_clamped(stream, dt, b.y, b.gu, 2 * e.ff, 0, e.ff, R * top, e.ff, e.limit, e.alpha));
+      HYB_OK(tha_hyb_linear(stream, dt, b.down, W, b.y, e.ff, 0, nullptr, e.w_down, (long long)W * e.ff, R * top, W, e.ff, b.group_off, e.experts));
+      if (e.shared_ff > 0) {
+        HYB_OK(tha_hyb_glu_clamped(stream, dt, b.sy, b.proj, ldp, e.o_sgate, e.o_sup, R, e.shared_ff, e.shared_limit, e.alpha));
+        HYB_OK(tha_hyb_linear(stream, dt, b.sdown, W, b.sy, e.shared_ff, 0, nullptr, e.w_sdown, 0, R, W, e.shared_ff, nullptr, 0));
+        sdown = b.sdown;
+      }
+    }
+    THA_CUDA_OK(launch(hyb_finish_kernel, dim3(R), dim3(128), 0, s, false, b.x, W, m->eps, (const float*)b.left, right, L.left_out, L.right_out, top,
+                       (const float*)b.weight, (const int*)b.inv, (const float*)b.down, sdown,
+                       taps ? taps + (size_t)li * R * W : (float*)nullptr));
+  }
+  if (n_want > 0 && logits) {
+    HYB_OK(tha_hyb_rmsnorm(stream, dt, b.hn, b.x, m->final_norm, 1.0f, m->eps, n_want, W, want_rows));
+    HYB_OK(tha_hyb_linear(stream, dt, logits, m->vocab, b.hn, W, 0, nullptr, m->head, 0, n_want, m->vocab, W, nullptr, 0));
+    if (m->logit_softcap > 0.f) {
+      const size_t n = (size_t)n_want * m->vocab;
+      THA_CUDA_OK(launch(hyb_softcap_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, false, logits, n, m->logit_softcap));
+    }
+  }
+  return THA_STATUS_SUCCESS;
+}

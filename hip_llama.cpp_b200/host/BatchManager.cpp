@@ -17,7 +17,24 @@ BatchManager::BatchManager(int batch_size_, int seq_len_, int n_layers_, int kv_
   mask_physical_KV_block.assign(batch_size, std::vector<bool>(nrow_blocks, false));
 }
 
-BatchManager::~BatchManager() { destroy_pool(); }
+BatchManager::~BatchManager() { destroy_pool(); destroy_state_slots(); }
+
+// ---- recurrent state slots ----------------------------------------------------------------------
+bool BatchManager::create_state_slots(size_t floats_per_slot) {
+  destroy_state_slots();
+  if (floats_per_slot < 1) return false;
+  const size_t bytes = (size_t)batch_size * floats_per_slot * sizeof(float);
+  if (tha_malloc((void**)&state_d_, bytes) != 0) { state_d_ = nullptr; return false; }
+  tha_memset(state_d_, 0, bytes);
+  state_floats_ = floats_per_slot;
+  return true;
+}
+
+void BatchManager::destroy_state_slots() {
+  if (state_d_) tha_free(state_d_);
+  state_d_ = nullptr;
+  state_floats_ = 0;
+}
 
 // ---- paged mode ---------------------------------------------------------------------------------
 bool BatchManager::create_pool(size_t n_blocks) {
@@ -128,6 +145,8 @@ int BatchManager::acquire_slot(int request_id) {
     if (logical_KV_table[s].first < 0) {
       logical_KV_table[s] = std::make_pair(request_id, 0);
       n_block_table_filled[s] = 0;
+      // blocking memset on the null stream: ordered after every earlier step that used the slot
+      if (state_d_) tha_memset(state_d_ + (size_t)s * state_floats_, 0, state_floats_ * sizeof(float));
       return s;
     }
   return -1;

@@ -1,0 +1,379 @@
+// The registry of architectures, the safetensors reader and the loader of layer-program models (include/layer_model.hpp).
+#include "layer_model.hpp"
+
+#include <fcntl.h>
+#include <math.h>
+#include <string.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <fstream>
+#include <mutex>
+#include <sstream>
+
+#include "tha_b200.h"
+
+void register_timerax();   // host/arch_timerax.cpp
+
+// ---- registry -----------------------------------------------------------------------------------------------------
+static std::vector<ArchitectureEntry>& registry() {
+  static std::vector<ArchitectureEntry> r;
+  return r;
+}
+static void register_builtin() {
+  static std::once_flag once;
+  std::call_once(once, [] {
+    registry().push_back({"llama2", ModelFamily::Llama2Checkpoint, nullptr});   // llama2.c v0 / v2 checkpoint files (host/utils.cpp)
+    register_timerax();
+  });
+}
+void register_architecture(const ArchitectureEntry& e) {
+  for (auto& x : registry())
+    if (x.name == e.name) { x = e; return; }
+  registry().push_back(e);
+}
+const ArchitectureEntry* find_architecture(const std::string& name) {
+  register_builtin();
+  for (auto& x : registry())
+    if (x.name == name) return &x;
+  return nullptr;
+}
+std::vector<std::string> registered_architectures() {
+  register_builtin();
+  std::vector<std::string> out;
+  for (auto& x : registry()) out.push_back(x.name);
+  return out;
+}
+const ArchitectureEntry* detect_model(const std::string& path, JsonValue* config, std::string* err) {
+  register_builtin();
+  struct stat sb;
+  if (stat(path.c_str(), &sb) != 0) { if (err) *err = "cannot open " + path; return nullptr; }
+  if (!S_ISDIR(sb.st_mode)) return find_architecture("llama2");
+  std::ifstream f(path + "/config.json");
+  if (!f) { if (err) *err = path + "/config.json is missing"; return nullptr; }
+  std::stringstream ss;
+  ss << f.rdbuf();
+  try {
+    JsonValue c = JsonValue::parse(ss.str());
+    const std::string name = c.at("architecture").string();
+    const ArchitectureEntry* e = find_architecture(name);
+    if (!e && err) {
+      *err = "architecture '" + name + "' is not registered (known:";
+      for (auto& n : registered_architectures()) *err += " " + n;
+      *err += ")";
+    }
+    if (config) *config = c;
+    return e;
+  } catch (const std::exception& ex) {
+    if (err) *err = ex.what();
+    return nullptr;
+  }
+}
+
+// ---- safetensors: 8-byte little-endian header length, JSON header, raw data ---------------------------------------
+bool SafeTensors::open(const std::string& path, std::string* err) {
+  const int fd = ::open(path.c_str(), O_RDONLY);
+  if (fd < 0) { if (err) *err = "cannot open " + path; return false; }
+  struct stat sb;
+  fstat(fd, &sb);
+  map_bytes_ = (size_t)sb.st_size;
+  map_ = mmap(nullptr, map_bytes_, PROT_READ, MAP_PRIVATE, fd, 0);
+  ::close(fd);
+  if (map_ == MAP_FAILED || map_bytes_ < 8) { map_ = nullptr; if (err) *err = "cannot map " + path; return false; }
+  const unsigned char* p = (const unsigned char*)map_;
+  uint64_t n = 0;
+  for (int i = 7; i >= 0; i--) n = (n << 8) | p[i];
+  if (8 + n > map_bytes_) { if (err) *err = path + ": bad header length"; return false; }
+  try {
+    JsonValue h = JsonValue::parse(std::string((const char*)p + 8, (size_t)n));
+    for (auto& kv : h.obj) {
+      if (kv.first == "__metadata__") continue;
+      TensorInfo t;
+      t.dtype = kv.second.at("dtype").string();
+      for (auto& d : kv.second.at("shape").arr) t.shape.push_back((long long)d.number());
+      t.begin = (size_t)kv.second.at("data_offsets").arr.at(0).number();
+      t.end = (size_t)kv.second.at("data_offsets").arr.at(1).number();
+      if (8 + n + t.end > map_bytes_ || t.begin > t.end) throw std::runtime_error("tensor '" + kv.first + "' lies outside the file");
+      index_[kv.first] = t;
+    }
+  } catch (const std::exception& ex) {
+    if (err) *err = path + ": " + ex.what();
+    return false;
+  }
+  data_ = p + 8 + n;
+  return true;
+}
+SafeTensors::~SafeTensors() { if (map_) munmap(map_, map_bytes_); }
+const TensorInfo& SafeTensors::info(const std::string& name) const {
+  auto it = index_.find(name);
+  if (it == index_.end()) throw std::runtime_error("tensor '" + name + "' is missing");
+  return it->second;
+}
+size_t SafeTensors::numel(const std::string& name) const {
+  size_t n = 1;
+  for (long long d : info(name).shape) n *= (size_t)d;
+  return n;
+}
+static inline float bf16_to_f32(uint16_t b) { uint32_t u = (uint32_t)b << 16; float f; memcpy(&f, &u, 4); return f; }
+static inline uint16_t f32_to_bf16(float f) {
+  uint32_t u; memcpy(&u, &f, 4);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x40);   // NaN stays NaN
+  u += 0x7fffu + ((u >> 16) & 1u);
+  return (uint16_t)(u >> 16);
+}
+void SafeTensors::read_f32(const std::string& name, std::vector<float>* out) const {
+  const TensorInfo& t = info(name);
+  const size_t n = numel(name);
+  const unsigned char* p = data_ + t.begin;
+  if (t.dtype == "BF16") {
+    if (t.end - t.begin != 2 * n) throw std::runtime_error("tensor '" + name + "': size does not fit its shape");
+    for (size_t i = 0; i < n; i++) { uint16_t b; memcpy(&b, p + 2 * i, 2); out->push_back(bf16_to_f32(b)); }
+  } else if (t.dtype == "F32") {
+    if (t.end - t.begin != 4 * n) throw std::runtime_error("tensor '" + name + "': size does not fit its shape");
+    for (size_t i = 0; i < n; i++) { float f; memcpy(&f, p + 4 * i, 4); out->push_back(f); }
+  } else {
+    throw std::runtime_error("tensor '" + name + "': dtype " + t.dtype + " is not served");
+  }
+}
+void SafeTensors::read_bf16(const std::string& name, std::vector<uint16_t>* out) const {
+  const TensorInfo& t = info(name);
+  const size_t n = numel(name);
+  const unsigned char* p = data_ + t.begin;
+  if (t.dtype == "BF16") {
+    if (t.end - t.begin != 2 * n) throw std::runtime_error("tensor '" + name + "': size does not fit its shape");
+    const size_t at = out->size();
+    out->resize(at + n);
+    memcpy(out->data() + at, p, 2 * n);
+  } else {
+    std::vector<float> f;
+    read_f32(name, &f);
+    for (float v : f) out->push_back(f32_to_bf16(v));
+  }
+}
+
+// ---- loader ---------------------------------------------------------------------------------------------------------
+LayerModel::~LayerModel() {
+  for (void* p : owned_) tha_free(p);
+}
+void* LayerModel::upload(const void* host, size_t bytes) {
+  void* d = nullptr;
+  if (tha_malloc(&d, bytes ? bytes : 16) != 0) throw std::runtime_error(std::string("device allocation failed: ") + tha_last_error());
+  owned_.push_back(d);
+  if (bytes && tha_memcpy_h2d(d, host, bytes) != 0) throw std::runtime_error(std::string("upload failed: ") + tha_last_error());
+  weight_bytes_ += bytes;
+  return d;
+}
+
+namespace {
+// matrices of one stack, in order; rows of each
+struct Stack {
+  const SafeTensors& file;
+  int dtype, cols;
+  std::vector<float> f;
+  std::vector<uint16_t> h;
+  int rows = 0;
+  Stack(const SafeTensors& file_, int dtype_, int cols_) : file(file_), dtype(dtype_), cols(cols_) {}
+  // returns the first row of the added matrix; checks [rows_expected, cols]
+  int add(const std::string& name, long long rows_expected) {
+    const TensorInfo& t = file.info(name);
+    const long long r = t.shape.size() == 2 ? t.shape[0] : -1, c = t.shape.size() == 2 ? t.shape[1] : -1;
+    if (r != rows_expected || c != cols)
+      throw std::runtime_error("tensor '" + name + "': shape [" + std::to_string(r) + ", " + std::to_string(c) + "] where [" +
+                               std::to_string(rows_expected) + ", " + std::to_string(cols) + "] is expected");
+    if (dtype == THA_DT_BF16) file.read_bf16(name, &h); else file.read_f32(name, &f);
+    const int at = rows;
+    rows += (int)r;
+    return at;
+  }
+  const void* data() const { return dtype == THA_DT_BF16 ? (const void*)h.data() : (const void*)f.data(); }
+  size_t bytes() const { return dtype == THA_DT_BF16 ? h.size() * 2 : f.size() * 4; }
+};
+}  // namespace
+
+LayerModel* LayerModel::load(const std::string& folder, int dtype, std::string* err) {
+  JsonValue config;
+  const ArchitectureEntry* e = detect_model(folder, &config, err);
+  if (!e) return nullptr;
+  if (e->family != ModelFamily::LayerProgram || !e->translate) { if (err) *err = "'" + e->name + "' is not a layer-program architecture"; return nullptr; }
+  LayerProgramSpec spec;
+  try {
+    e->translate(config, &spec);
+  } catch (const std::exception& ex) {
+    if (err) *err = ex.what();
+    return nullptr;
+  }
+  SafeTensors file;
+  if (!file.open(folder + "/model.safetensors", err)) return nullptr;
+  return build(spec, file, dtype, err);
+}
+
+LayerModel* LayerModel::build(const LayerProgramSpec& spec, const SafeTensors& file, int dtype, std::string* err) {
+  LayerModel* m = new LayerModel();
+  try {
+    m->spec_ = spec;
+    const int W = spec.width;
+    auto vec = [&](const std::string& name, size_t n) -> const float* {
+      std::vector<float> v;
+      file.read_f32(name, &v);
+      if (v.size() != n) throw std::runtime_error("tensor '" + name + "': " + std::to_string(v.size()) + " values where " + std::to_string(n) + " are expected");
+      return (const float*)m->upload(v.data(), v.size() * 4);
+    };
+    auto mat = [&](const std::string& name, long long rows, int cols) -> const void* {
+      Stack s(file, dtype, cols);
+      s.add(name, rows);
+      return m->upload(s.data(), s.bytes());
+    };
+    m->layers_.resize(spec.layers.size());
+    long long state = 0;
+    for (size_t li = 0; li < spec.layers.size(); li++) {
+      const LayerSpec& ls = spec.layers[li];
+      tha_hyb_layer_t& L = m->layers_[li];
+      memset(&L, 0, sizeof(L));
+      L.mixer = ls.mixer;
+      L.norm1 = vec(ls.norm1, W);
+      Stack in(file, dtype, W);
+      if (ls.mixer == THA_MIX_PARALLEL) {
+        const AttnSpec& a = ls.attn;
+        if (a.heads < 1 || a.kv_heads < 1 || a.heads % a.kv_heads) throw std::runtime_error("attention: heads must be a multiple of kv_heads");
+        tha_attn_t& A = L.attn;
+        A.heads = a.heads; A.kv_heads = a.kv_heads; A.dim = a.dim; A.vdim = a.vdim;
+        A.unit_rms = a.unit_rms; A.eps = spec.eps; A.scale = a.scale; A.chunk = a.chunk;
+        A.rot = -1;
+        if (a.rotary && a.rot.dims > 0) {
+          if (a.rot.dims > a.dim || (a.rot.dims & 1)) throw std::runtime_error("attention: rotated dimensions must be even and at most dim");
+          size_t r = 0;
+          while (r < m->rot_specs_.size() && !(m->rot_specs_[r] == a.rot)) r++;
+          if (r == m->rot_specs_.size()) {
+            // inverse frequencies in float64: base^(-2i/dims), interpolated between the original and the stretched scale
+            const int dims = a.rot.dims, half = dims / 2;
+            std::vector<double> f(half);
+            for (int i = 0; i < half; i++) f[i] = pow(a.rot.base, -2.0 * i / dims);
+            float mag = 1.0f;
+            if (a.rot.yarn) {
+              auto where = [&](double turns) { return dims * log(a.rot.original / (2.0 * M_PI * turns)) / (2.0 * log(a.rot.base)); };
+              const double lo = fmax(floor(where(a.rot.fast)), 0.0), hi = fmin(ceil(where(a.rot.slow)), dims - 1.0);
+              for (int i = 0; i < half; i++) {
+                const double ramp = fmin(fmax((i - lo) / fmax(hi - lo, 0.001), 0.0), 1.0);
+                f[i] = f[i] / a.rot.factor * ramp + f[i] * (1.0 - ramp);
+              }
+              mag = (float)(0.1 * log(a.rot.factor) + 1.0);
+            }
+            tha_rotary_t R;
+            R.inv_freq = (const double*)m->upload(f.data(), f.size() * 8);
+            R.dims = dims;
+            R.mag = mag;
+            m->rot_.push_back(R);
+            m->rot_specs_.push_back(a.rot);
+          }
+          A.rot = (int)r;
+        }
+        A.cache_layer = m->n_cache_layers_++;
+        m->kv_dim_ = std::max(m->kv_dim_, std::max(a.kv_heads * a.dim, a.kv_heads * a.vdim));
+        A.o_q = in.add(a.q, (long long)a.heads * a.dim);
+        A.o_k = in.add(a.k, (long long)a.kv_heads * a.dim);
+        A.o_v = in.add(a.v, (long long)a.kv_heads * a.vdim);
+        A.w_o = mat(a.o, W, a.heads * a.vdim);
+        const MemSpec& r = ls.mem;
+        tha_mem_t& M = L.mem;
+        M.heads = r.heads; M.dim = r.dim; M.vdim = r.vdim; M.gate_cap = r.gate_cap; M.eps = spec.eps;
+        M.o_q = in.add(r.q, (long long)r.heads * r.dim);
+        M.o_k = in.add(r.k, (long long)r.heads * r.dim);
+        M.o_v = in.add(r.v, (long long)r.heads * r.vdim);
+        M.o_g = in.add(r.g, (long long)r.heads * r.vdim);
+        M.o_i = in.add(r.i, r.heads);
+        M.o_f = in.add(r.f, r.heads);
+        M.b_i = vec(r.i_b, r.heads);
+        M.b_f = vec(r.f_b, r.heads);
+        M.norm = vec(r.norm, (size_t)r.heads * r.vdim);
+        M.w_o = mat(r.o, W, r.heads * r.vdim);
+        M.state_off = state;
+        state += (long long)r.heads * ((long long)r.dim * r.vdim + r.dim + 1);
+        L.left_out = vec(ls.left_out, W);
+        L.right_out = vec(ls.right_out, W);
+      } else if (ls.mixer == THA_MIX_DELTA) {
+        const DeltaSpec& d = ls.delta;
+        if (d.heads < 1 || d.kv_heads < 1 || d.heads % d.kv_heads || d.taps < 1) throw std::runtime_error("delta rule: heads must be a multiple of kv_heads, taps >= 1");
+        tha_delta_t& D = L.delta;
+        D.heads = d.heads; D.kv_heads = d.kv_heads; D.dim = d.dim; D.vdim = d.vdim; D.taps = d.taps; D.eps = spec.eps;
+        const TensorInfo& a1 = file.info(d.a1);
+        const TensorInfo& g1 = file.info(d.g1);
+        if (a1.shape.size() != 2 || g1.shape.size() != 2) throw std::runtime_error("delta rule: the low-rank projections must be matrices");
+        D.rank_a = (int)a1.shape[0];
+        D.rank_g = (int)g1.shape[0];
+        const long long cq = (long long)d.kv_heads * d.dim, cv = (long long)d.heads * d.vdim;
+        D.o_q = in.add(d.q, cq);
+        in.add(d.k, cq);
+        in.add(d.v, cv);
+        D.o_b = in.add(d.b, d.heads);
+        D.o_a1 = in.add(d.a1, D.rank_a);
+        D.o_g1 = in.add(d.g1, D.rank_g);
+        std::vector<float> taps;
+        file.read_f32(d.q_conv, &taps);
+        file.read_f32(d.k_conv, &taps);
+        file.read_f32(d.v_conv, &taps);
+        if ((long long)taps.size() != (2 * cq + cv) * d.taps) throw std::runtime_error("delta rule: convolution taps do not fit [channels, " + std::to_string(d.taps) + "]");
+        D.conv = (const float*)m->upload(taps.data(), taps.size() * 4);
+        D.w_a2 = mat(d.a2, (long long)d.heads * d.dim, D.rank_a);
+        D.w_g2 = mat(d.g2, cv, D.rank_g);
+        D.a_log = vec(d.a_log, d.heads);
+        D.dt_bias = vec(d.dt_bias, (size_t)d.heads * d.dim);
+        D.norm = vec(d.norm, d.vdim);
+        D.w_o = mat(d.o, W, (int)cv);
+        D.state_off = state;
+        state += (long long)d.heads * d.dim * d.vdim;
+        D.conv_state_off = state;
+        state += (2 * cq + cv) * (d.taps - 1);
+      } else {
+        throw std::runtime_error("unknown mixer kind");
+      }
+      L.has_ff = ls.has_ff ? 1 : 0;
+      if (ls.has_ff) {
+        const MoeSpec& e = ls.moe;
+        if (e.top < 1 || e.top > e.experts || e.top > 32) throw std::runtime_error("mixture of experts: 1 <= top <= min(experts, 32)");
+        tha_moe_t& E = L.moe;
+        E.experts = e.experts; E.top = e.top; E.ff = e.ff; E.limit = e.limit; E.alpha = e.alpha;
+        E.o_router = in.add(e.router, e.experts);
+        Stack gu(file, dtype, W), dn(file, dtype, e.ff);
+        for (int x = 0; x < e.experts; x++) {
+          const std::string p = e.prefix + "e" + std::to_string(x) + ".";
+          gu.add(p + "gate", e.ff);
+          gu.add(p + "up", e.ff);
+          dn.add(p + "down", W);
+        }
+        E.w_gate_up = m->upload(gu.data(), gu.bytes());
+        E.w_down = m->upload(dn.data(), dn.bytes());
+        E.shared_ff = e.shared_ff;
+        E.shared_limit = e.shared_limit;
+        if (e.shared_ff > 0) {
+          E.o_sgate = in.add(e.s_gate, e.shared_ff);
+          E.o_sup = in.add(e.s_up, e.shared_ff);
+          E.w_sdown = mat(e.s_down, W, e.shared_ff);
+        }
+      }
+      L.n_in = in.rows;
+      L.w_in = m->upload(in.data(), in.bytes());
+    }
+    m->state_floats_ = state > 0 ? state : 1;
+    if (m->rot_.size() > 16) throw std::runtime_error("more than 16 distinct rotary tables");
+    tha_hyb_model_t& M = m->model_;
+    M.dtype = dtype;
+    M.width = W;
+    M.vocab = spec.vocab;
+    M.n_layers = (int)m->layers_.size();
+    M.eps = spec.eps;
+    M.logit_softcap = spec.logit_softcap;
+    M.embed = mat(spec.embed, spec.vocab, W);
+    M.final_norm = vec(spec.final_norm, W);
+    M.head = mat(spec.head, spec.vocab, W);
+    M.layers = m->layers_.data();
+    M.n_rot = (int)m->rot_.size();
+    M.rot = m->rot_.data();
+    if (m->kv_dim_ < 1) m->kv_dim_ = 1;
+    return m;
+  } catch (const std::exception& ex) {
+    if (err) *err = ex.what();
+    delete m;
+    return nullptr;
+  }
+}

@@ -81,6 +81,18 @@ class BatchManager {
   bool ensure_position(int seq_id, int pos);      // the blocks covering positions 0..pos exist (false: pool exhausted)
   void sync_table(void* stream);                  // upload table rows that changed since the last call (stream-ordered)
   const int* host_table() const { return table_h_.data(); }
+  const int* device_table() const { return table_d_; }
+  float* pool_k() const { return pool_k_; }
+  float* pool_v() const { return pool_v_; }
+
+  // ---- recurrent state slots -------------------------------------------------------------------
+  // Models whose layers carry a fixed-size state from token to token (matrix memories, delta-rule memories, convolution
+  // tails) get one fp32 region per slot beside the block pool.  A slot is zeroed when a request takes it (acquire_slot):
+  // the state of a sequence starts at zero, and nothing of the slot's previous request may survive.
+  bool create_state_slots(size_t floats_per_slot);
+  void destroy_state_slots();
+  float* state_base() const { return state_d_; }
+  size_t state_slot_floats() const { return state_floats_; }
 
  private:
   RunState* bound_;
@@ -91,4 +103,6 @@ class BatchManager {
   std::vector<int> table_h_;                      // [batch_size][nrow_blocks]
   std::vector<int> free_list_;
   std::vector<char> dirty_;                       // per slot
+  float* state_d_ = nullptr;                      // [batch_size][state_floats_]
+  size_t state_floats_ = 0;
 };

@@ -1,0 +1,132 @@
+// layer_model.hpp -- models described by data: the registry of architectures, the description a config.json is
+// translated into, and the loader that turns description + tensor file into device-resident tha_hyb_model_t.
+//
+// The llama2 family (include/models.hpp) is one fixed struct read from a llama2.c checkpoint.  A layer-program model is
+// a folder with config.json and model.safetensors; its "architecture" key picks a translator from the registry, which
+// names, layer by layer, the mechanisms (include/tha_hybrid.h) with their sizes, constants and tensor names.  A new
+// design that combines the same mechanisms differently registers another translator; a new mechanism is added to
+// tha_hybrid.h once and becomes available to every translator.
+#pragma once
+#include <stdint.h>
+
+#include <map>
+#include <string>
+#include <vector>
+
+#include "json_min.hpp"
+#include "tha_hybrid.h"
+
+// ---- description (host side, tensor NAMES instead of pointers) --------------------------------------------------------
+struct RotarySpec {
+  int dims = 0;
+  double base = 10000.0;
+  bool yarn = false;          // frequency interpolation between a fast and a slow wavelength bound
+  double factor = 1.0, original = 0.0, fast = 32.0, slow = 1.0;
+  bool operator==(const RotarySpec& o) const {
+    return dims == o.dims && base == o.base && yarn == o.yarn && factor == o.factor && original == o.original && fast == o.fast &&
+           slow == o.slow;
+  }
+};
+struct AttnSpec {
+  int heads = 0, kv_heads = 0, dim = 0, vdim = 0, chunk = 0;
+  bool rotary = false, unit_rms = false;
+  RotarySpec rot;
+  float scale = 1.0f;
+  std::string q, k, v, o;
+};
+struct MemSpec {
+  int heads = 0, dim = 0, vdim = 0;
+  float gate_cap = 15.0f;
+  std::string q, k, v, g, o, norm, i, i_b, f, f_b;
+};
+struct DeltaSpec {
+  int heads = 0, kv_heads = 0, dim = 0, vdim = 0, taps = 1;
+  std::string q, k, v, q_conv, k_conv, v_conv, b, a_log, norm, a1, a2, dt_bias, g1, g2, o;
+};
+struct MoeSpec {
+  int experts = 0, top = 0, ff = 0, shared_ff = 0;
+  float limit = 0.f, shared_limit = 0.f, alpha = 1.702f;
+  std::string router, prefix;            // expert e's tensors: prefix + "e<e>.gate" / ".up" / ".down"
+  std::string s_gate, s_up, s_down;
+};
+struct LayerSpec {
+  int mixer = THA_MIX_PARALLEL;
+  std::string norm1;
+  AttnSpec attn;
+  MemSpec mem;
+  std::string left_out, right_out;
+  DeltaSpec delta;
+  bool has_ff = false;
+  MoeSpec moe;
+};
+struct LayerProgramSpec {
+  int width = 0, vocab = 0;
+  float eps = 1e-5f, logit_softcap = 0.f;
+  std::string embed, final_norm, head;
+  std::vector<LayerSpec> layers;
+};
+
+// ---- registry -----------------------------------------------------------------------------------------------------
+enum class ModelFamily { Llama2Checkpoint, LayerProgram };
+struct ArchitectureEntry {
+  std::string name;
+  ModelFamily family;
+  // LayerProgram: fill `out` from the parsed config.json; throw std::runtime_error on a config it cannot serve
+  void (*translate)(const JsonValue& config, LayerProgramSpec* out);
+};
+void register_architecture(const ArchitectureEntry& e);
+const ArchitectureEntry* find_architecture(const std::string& name);
+std::vector<std::string> registered_architectures();
+// A folder with config.json -> the entry its "architecture" names (config parsed into *config); a llama2.c checkpoint
+// file -> the "llama2" entry.  nullptr + *err when neither.
+const ArchitectureEntry* detect_model(const std::string& path, JsonValue* config, std::string* err);
+
+// ---- tensor file ----------------------------------------------------------------------------------------------------
+struct TensorInfo { std::string dtype; std::vector<long long> shape; size_t begin = 0, end = 0; };
+class SafeTensors {
+ public:
+  bool open(const std::string& path, std::string* err);
+  ~SafeTensors();
+  bool has(const std::string& name) const { return index_.count(name) > 0; }
+  const TensorInfo& info(const std::string& name) const;
+  size_t numel(const std::string& name) const;
+  // append the tensor's values to `out` as fp32 / as raw bf16 bit patterns (rounding fp32 to nearest even)
+  void read_f32(const std::string& name, std::vector<float>* out) const;
+  void read_bf16(const std::string& name, std::vector<uint16_t>* out) const;
+
+ private:
+  std::map<std::string, TensorInfo> index_;
+  const unsigned char* data_ = nullptr;   // start of the data section inside the mapping
+  void* map_ = nullptr;
+  size_t map_bytes_ = 0;
+};
+
+// ---- the loaded model ---------------------------------------------------------------------------------------------
+class LayerModel {
+ public:
+  // dtype: THA_DT_BF16 or THA_DT_F32.  Uploads to the current device.
+  static LayerModel* load(const std::string& folder, int dtype, std::string* err);
+  static LayerModel* build(const LayerProgramSpec& spec, const SafeTensors& file, int dtype, std::string* err);
+  ~LayerModel();
+
+  const tha_hyb_model_t* device_model() const { return &model_; }
+  const LayerProgramSpec& spec() const { return spec_; }
+  int vocab() const { return spec_.vocab; }
+  int n_cache_layers() const { return n_cache_layers_; }
+  int kv_dim() const { return kv_dim_; }                    // widest K or V row (floats)
+  long long state_floats() const { return state_floats_; }  // recurrent state of one sequence
+  size_t weight_bytes() const { return weight_bytes_; }
+
+ private:
+  LayerModel() {}
+  void* upload(const void* host, size_t bytes);
+  LayerProgramSpec spec_;
+  tha_hyb_model_t model_ = {};
+  std::vector<tha_hyb_layer_t> layers_;
+  std::vector<tha_rotary_t> rot_;
+  std::vector<RotarySpec> rot_specs_;
+  std::vector<void*> owned_;
+  int n_cache_layers_ = 0, kv_dim_ = 0;
+  long long state_floats_ = 0;
+  size_t weight_bytes_ = 0;
+};

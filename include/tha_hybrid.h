@@ -1,0 +1,206 @@
+/* tha_hybrid.h -- C-ABI of the layer-program path: decoder models whose layers are described by data
+ * (which sequence mixer, which feed-forward, every size and constant) instead of by a fixed struct.
+ *
+ * The llama2 path (tha_b200.h) hard-wires one layer shape.  Here a model is an array of tha_hyb_layer_t, each naming
+ * its mixer(s) and feed-forward; tha_hyb_step runs ONE scheduler step over a ragged batch of rows (a row = one token
+ * of one sequence at one position): prompt portions of some sequences beside single decoded tokens of others.  What a
+ * sequence carries from step to step lives in two stores the host's BatchManager owns:
+ *   - cache rows of the softmax-attention layers in a block pool addressed through a block table (paged KV), and
+ *   - one fixed-size fp32 state slot per live sequence for the recurrent mixers (matrix memories, delta-rule
+ *     memories, the tails of the short convolutions).
+ * Every mechanism is also callable by itself (tha_hyb_* ops below) so that it can be tested alone and reused by
+ * another layer description.
+ *
+ * Number formats: `dtype` selects the storage type of matrices and of the vectors that enter a matrix product
+ * (THA_DT_BF16: bf16 with fp32 accumulation; THA_DT_F32: plain fp32 FMA, no reduced-precision matrix mode).  The
+ * residual stream, norms, softmax, routers, gates, decays and all recurrent state are fp32 in both.
+ * Small vectors (norm weights, biases, convolution taps, decay parameters) are always fp32 device arrays.
+ * Matrices are row-major [out, in].  All pointers are device pointers unless named *_host.
+ */
+#ifndef THA_HYBRID_H
+#define THA_HYBRID_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define THA_DT_BF16 0
+#define THA_DT_F32 1
+
+#define THA_MIX_PARALLEL 0 /* softmax attention and a matrix memory side by side, outputs normed and averaged */
+#define THA_MIX_DELTA 1    /* gated delta rule with per-channel decay */
+
+/* The rows of one step.  Rows of a sequence are consecutive and in ascending position. */
+typedef struct {
+  int n_rows, n_seqs;
+  const int* token;     /* [n_rows] */
+  const int* pos;       /* [n_rows] position of the row in its sequence (from 0) */
+  const int* row_seq;   /* [n_rows] index of the row's sequence in this step (0..n_seqs-1) */
+  const int* seq_first; /* [n_seqs + 1] first row of each sequence; seq_first[n_seqs] == n_rows */
+  const int* seq_slot;  /* [n_seqs] slot of the sequence: its block-table row and its state slot */
+  int max_seq_rows;     /* longest portion of the step */
+  int max_pos;          /* largest position of the step */
+} tha_rows_t;
+
+/* Paged cache: pools [block][cache layer][position in block][kv_dim] fp32, one table row of block ids per slot. */
+typedef struct {
+  float* k_pool;
+  float* v_pool;
+  const int* table;
+  int table_stride; /* blocks per slot */
+  int block_size;   /* positions per block, a power of two */
+  int n_cache_layers;
+  int kv_dim;       /* row pitch in floats (the widest K or V row of the model) */
+} tha_kv_t;
+
+/* Recurrent state: slot s starts at base + s * slot_floats. */
+typedef struct {
+  float* base;
+  long long slot_floats;
+} tha_state_store_t;
+
+/* Rotary position tables: angle = position * inv_freq[i] (float64 on the device), cos and sin times `mag`. */
+typedef struct {
+  const double* inv_freq; /* [dims / 2] */
+  int dims;               /* rotated dimensions of a head (pairs 2i, 2i+1), the rest pass unchanged */
+  float mag;
+} tha_rotary_t;
+
+/* Softmax attention over the cache.  A query at position p sees the keys j <= p with
+ * floor(j / chunk) == floor(p / chunk) when chunk > 0, every j <= p otherwise. */
+typedef struct {
+  int heads, kv_heads, dim, vdim;
+  int rot;          /* index into the model's rotary tables, -1: none */
+  int unit_rms;     /* 1: q and k are divided by their root mean square over dim after rotation */
+  float eps;
+  float scale;
+  int chunk;
+  int cache_layer;  /* which layer of the pool holds this layer's rows */
+  int o_q, o_k, o_v; /* columns of the stacked input projection */
+  const void* w_o;  /* [width, heads * vdim] */
+} tha_attn_t;
+
+/* Matrix memory with exponential input gate, sigmoid forget gate (both in log space, soft-capped) and a running
+ * maximum that starts at 0.  State per head: S [dim, vdim], n [dim], m. */
+typedef struct {
+  int heads, dim, vdim;
+  float gate_cap, eps;
+  int o_q, o_k, o_v, o_g, o_i, o_f;
+  const float* b_i; /* [heads] */
+  const float* b_f; /* [heads] */
+  const float* norm; /* [heads * vdim] */
+  const void* w_o;  /* [width, heads * vdim] */
+  long long state_off; /* floats from the slot's start */
+} tha_mem_t;
+
+/* Gated delta rule.  q / k have kv_heads heads of dim, v has heads heads of vdim; a short causal convolution
+ * (taps, silu) runs over q | k | v, which are adjacent columns of the stacked projection starting at o_q.
+ * State per head: S [dim, vdim]; plus the last taps-1 inputs of every convolved channel. */
+typedef struct {
+  int heads, kv_heads, dim, vdim, taps, rank_a, rank_g;
+  float eps;
+  int o_q, o_b, o_a1, o_g1; /* columns of the stacked projection (k follows q, v follows k) */
+  const float* conv;   /* [channels, taps], channels = 2 * kv_heads * dim + heads * vdim */
+  const void* w_a2;    /* [heads * dim, rank_a] */
+  const void* w_g2;    /* [heads * vdim, rank_g] */
+  const float* a_log;  /* [heads] */
+  const float* dt_bias; /* [heads * dim] */
+  const float* norm;   /* [vdim] */
+  const void* w_o;     /* [width, heads * vdim] */
+  long long state_off, conv_state_off;
+} tha_delta_t;
+
+/* Mixture of experts with clamped gated activation: g = min(gate, limit), u = clamp(up, -limit, limit),
+ * y = g * sigmoid(alpha * g) * (u + 1).  Router: top-k logits, softmax over the chosen.  Optional shared expert. */
+typedef struct {
+  int experts, top, ff;
+  float limit, alpha;
+  int o_router;
+  const void* w_gate_up; /* [experts][2 * ff, width]: an expert's gate rows, then its up rows */
+  const void* w_down;    /* [experts][width, ff] */
+  int shared_ff;         /* 0: none */
+  float shared_limit;
+  int o_sgate, o_sup;
+  const void* w_sdown;   /* [width, shared_ff] */
+} tha_moe_t;
+
+typedef struct {
+  int mixer;            /* THA_MIX_* */
+  const float* norm1;   /* [width] stored around zero: the factor is 1 + w */
+  const void* w_in;     /* every matrix that reads the normed input, stacked: [n_in, width] */
+  int n_in;
+  tha_attn_t attn;      /* THA_MIX_PARALLEL */
+  tha_mem_t mem;        /* THA_MIX_PARALLEL */
+  const float* left_out;  /* [width] weights of the two sides' output norms */
+  const float* right_out;
+  tha_delta_t delta;    /* THA_MIX_DELTA */
+  int has_ff;
+  tha_moe_t moe;
+} tha_hyb_layer_t;
+
+typedef struct {
+  int dtype;
+  int width, vocab, n_layers;
+  float eps;
+  float logit_softcap;  /* 0: none */
+  const void* embed;    /* [vocab, width] */
+  const float* final_norm;
+  const void* head;     /* [vocab, width] */
+  const tha_hyb_layer_t* layers; /* host array */
+  int n_rot;
+  const tha_rotary_t* rot;       /* host array */
+} tha_hyb_model_t;
+
+/* One scheduler step: every row through every layer; logits [n_want, vocab] (fp32) of the rows listed in want_rows.
+ * `taps`, when not NULL, receives the residual stream after every layer: [n_layers, n_rows, width] fp32.
+ * Stream-ordered; scratch is owned by the library and grows outside of any capture. */
+int tha_hyb_step(void* stream, const tha_hyb_model_t* m, const tha_rows_t* rows, const tha_kv_t* kv,
+                 const tha_state_store_t* st, int n_want, const int* want_rows, float* logits, float* taps);
+
+/* ---- the mechanisms, one call each (also what tha_hyb_step is made of) ------------------------------------------- */
+/* out[r, :] = x[r, :] / sqrt(mean(x[r]^2) + eps) * (w_offset + w), rows picked through `rows_idx` when not NULL;
+ * out is dtype-typed (bf16 / fp32) */
+int tha_hyb_rmsnorm(void* stream, int dtype, void* out, const float* x, const float* w, float w_offset, float eps,
+                    int n_rows, int width, const int* rows_idx);
+/* C[m, 0:N] = A[row(m), 0:K] . W_g[0:N, 0:K]^T, fp32 out.  a_f32: A is fp32 (else dtype-typed).  gather: row(m) =
+ * a_rows[m] (NULL: m).  Groups: rows group_off[g] .. group_off[g+1]-1 use the matrix W + g * w_group_stride elements
+ * (group_off NULL: one group of M rows). */
+int tha_hyb_linear(void* stream, int dtype, float* C, long long ldc, const void* A, long long lda, int a_f32,
+                   const int* a_rows, const void* W, long long w_group_stride, int M, int N, int K,
+                   const int* group_off, int n_groups);
+/* cos / sin [n_rows, dims/2] of the rows' positions */
+int tha_hyb_rotary_table(void* stream, const tha_rotary_t* rot, const int* pos, int n_rows, float* cos_out, float* sin_out);
+/* rotate q and k, unit-rms them, write k and v to the cache rows of (slot, pos), q to q_out [n_rows, heads * dim] */
+int tha_hyb_attn_prepare(void* stream, const tha_attn_t* a, const tha_rows_t* rows, const tha_kv_t* kv, const float* proj,
+                         long long ldp, const float* cos_t, const float* sin_t, int rot_dims, float* q_out);
+/* softmax attention of every row over its visible cache rows; out dtype-typed [n_rows, heads * vdim] */
+int tha_hyb_attn(void* stream, int dtype, const tha_attn_t* a, const tha_rows_t* rows, const tha_kv_t* kv, const float* q,
+                 void* out);
+/* the matrix memory over the rows of every sequence in order, state read from and written back to the slots;
+ * out dtype-typed [n_rows, heads * vdim] = unit-rms per head * norm * sigmoid(gate) */
+int tha_hyb_mem_scan(void* stream, int dtype, const tha_mem_t* m, const tha_rows_t* rows, const tha_state_store_t* st,
+                     const float* proj, long long ldp, void* out);
+/* causal convolution + silu over `channels` adjacent columns of proj starting at col0, continuing from the slot's
+ * tail; out fp32 [n_rows, channels]; then the tails are advanced */
+int tha_hyb_conv_silu(void* stream, const tha_rows_t* rows, const tha_state_store_t* st, long long conv_state_off,
+                      const float* proj, long long ldp, int col0, int channels, int taps, const float* w, float* out);
+/* the gated delta rule over the rows of every sequence in order; qkv = the convolved q | k | v, dt_raw [n_rows, heads*dim]
+ * and gate_raw [n_rows, heads*vdim] the outputs of the two low-rank projections (before bias / softplus / sigmoid) */
+int tha_hyb_delta_scan(void* stream, int dtype, const tha_delta_t* d, const tha_rows_t* rows, const tha_state_store_t* st,
+                       const float* qkv, const float* proj, long long ldp, const float* dt_raw, const float* gate_raw,
+                       void* out);
+/* router: expert ids and weights [n_rows, top]; rows sorted by expert: group_off (2 * (experts + 1) ints: the offsets,
+ * then scratch), sorted_row [n_rows * top] and the position of (row, j) in that order, inv [n_rows * top] */
+int tha_hyb_moe_route(void* stream, const tha_moe_t* e, const float* proj, long long ldp, int n_rows, int* expert_id,
+                      float* weight, int* group_off, int* sorted_row, int* inv);
+/* y = g * sigmoid(alpha g) * (u + 1) with the clamps; gu [n, ldg] holds gate at col_g and up at col_u; y dtype-typed [n, ff] */
+int tha_hyb_glu_clamped(void* stream, int dtype, void* y, const float* gu, long long ldg, int col_g, int col_u, int n,
+                        int ff, float limit, float alpha);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
