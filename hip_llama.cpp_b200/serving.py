@@ -1,0 +1,229 @@
+"""Python binding of the layer-program serving path (include/tha_engine.h in lib/libthablas.so), plus the writers of
+model folders that tests and benchmarks use.
+
+    eng = ServingEngine(folder, "float32", max_tokens=2048, max_seqs=4)
+    logits = eng.step([("a", [5, 17, 3], [0, 2]), ("b", [9], [0])])      # [3, vocab]
+    eng.finish("a")
+    out = eng.generate([[1, 2, 3], [4, 5]], max_new=[8, 8])              # greedy through the scheduler
+
+Everything that computes runs in the C++ / CUDA libraries; there is no fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import json
+import os
+import struct
+
+import numpy as np
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+HOST_LIB_PATH = os.path.join(PKG, "lib", "libthablas.so")
+DTYPES = {"bfloat16": 0, "bf16": 0, "float32": 1, "f32": 1}
+
+_host = None
+
+
+def host_lib():
+    global _host
+    if _host is None:
+        if not os.path.exists(HOST_LIB_PATH):
+            raise RuntimeError(f"{HOST_LIB_PATH} is missing: run `python hip_llama.cpp_b200/build.py`")
+        lib = C.CDLL(HOST_LIB_PATH)
+        vp, I = C.c_void_p, C.c_int
+        lib.thaEngineOpen.argtypes = [C.c_char_p, I, I, I, C.POINTER(vp)]
+        lib.thaEngineOpenError.restype = C.c_char_p
+        lib.thaEngineError.restype = C.c_char_p
+        lib.thaEngineError.argtypes = [vp]
+        lib.thaEngineClose.argtypes = [vp]
+        lib.thaEngineClose.restype = None
+        for n in ("thaEngineVocab", "thaEngineWidth", "thaEngineLayers"):
+            getattr(lib, n).argtypes = [vp]
+        lib.thaEngineFreeBlocks.argtypes = [vp]
+        lib.thaEngineFreeBlocks.restype = C.c_longlong
+        lib.thaEngineSteps.argtypes = [vp]
+        lib.thaEngineSteps.restype = C.c_longlong
+        lib.thaEngineSlot.argtypes = [vp, C.c_char_p]
+        lib.thaEngineStep.argtypes = [vp, I, C.POINTER(C.c_char_p), vp, vp, vp, vp, vp, vp]
+        lib.thaEngineFinish.argtypes = [vp, C.c_char_p]
+        lib.thaEngineGenerate.argtypes = [vp, I, vp, vp, vp, C.c_float, C.c_float, C.c_ulonglong, I, vp]
+        _host = lib
+    return _host
+
+
+class ServingError(RuntimeError):
+    pass
+
+
+class ServingEngine:
+    """A model folder on the current GPU with its block pool and state slots."""
+
+    def __init__(self, folder: str, dtype: str = "bfloat16", max_tokens: int = 4096, max_seqs: int = 4):
+        self.lib = host_lib()
+        self.h = C.c_void_p()
+        st = self.lib.thaEngineOpen(os.fspath(folder).encode(), DTYPES[dtype], max_tokens, max_seqs, C.byref(self.h))
+        if st != 0:
+            self.h = None
+            raise ServingError(self.lib.thaEngineOpenError().decode())
+        self.vocab = self.lib.thaEngineVocab(self.h)
+        self.width = self.lib.thaEngineWidth(self.h)
+        self.layers = self.lib.thaEngineLayers(self.h)
+
+    def close(self):
+        if self.h:
+            self.lib.thaEngineClose(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def step(self, entries, taps: bool = False):
+        """entries: [(id, tokens, want), ...].  Returns logits [wanted, vocab] (and the residual stream after every
+        layer, [layers, rows, width], with taps=True)."""
+        n = len(entries)
+        ids = (C.c_char_p * n)(*[e[0].encode() for e in entries])
+        counts = np.array([len(e[1]) for e in entries], np.int32)
+        tokens = np.array([t for e in entries for t in e[1]], np.int32)
+        wc = np.array([len(e[2]) for e in entries], np.int32)
+        wants = np.array([w for e in entries for w in e[2]], np.int32)
+        logits = np.zeros((int(wc.sum()), self.vocab), np.float32)
+        tp = np.zeros((self.layers, int(counts.sum()), self.width), np.float32) if taps else None
+        st = self.lib.thaEngineStep(self.h, n, ids, counts.ctypes.data, tokens.ctypes.data, wc.ctypes.data, wants.ctypes.data,
+                                    logits.ctypes.data, tp.ctypes.data if taps else None)
+        if st != 0:
+            raise ServingError(self.lib.thaEngineError(self.h).decode())
+        return (logits, tp) if taps else logits
+
+    def finish(self, rid: str):
+        self.lib.thaEngineFinish(self.h, rid.encode())
+
+    def slot(self, rid: str) -> int:
+        return self.lib.thaEngineSlot(self.h, rid.encode())
+
+    def free_blocks(self) -> int:
+        return int(self.lib.thaEngineFreeBlocks(self.h))
+
+    def steps_run(self) -> int:
+        return int(self.lib.thaEngineSteps(self.h))
+
+    def generate(self, prompts, max_new, temperature: float = 0.0, topp: float = 0.9, seed: int = 1, portion: int = 256):
+        lens = np.array([len(p) for p in prompts], np.int32)
+        flat = np.array([t for p in prompts for t in p], np.int32)
+        mn = np.array(max_new, np.int32)
+        out = np.zeros(int(mn.sum()), np.int32)
+        st = self.lib.thaEngineGenerate(self.h, len(prompts), lens.ctypes.data, flat.ctypes.data, mn.ctypes.data, temperature, topp, seed,
+                                        portion, out.ctypes.data)
+        if st != 0:
+            raise ServingError(self.lib.thaEngineError(self.h).decode())
+        res, at = [], 0
+        for k in mn:
+            res.append(out[at:at + k].tolist())
+            at += k
+        return res
+
+
+# ---- model folders --------------------------------------------------------------------------------------------------
+def _to_bf16_bits(a: np.ndarray) -> np.ndarray:
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    return (((u + 0x7FFF + ((u >> 16) & 1)) >> 16) & 0xFFFF).astype(np.uint16)
+
+
+def save_model_folder(folder: str, config: dict, tensors: dict) -> None:
+    """config.json + model.safetensors (every tensor as bfloat16, round to nearest even)."""
+    os.makedirs(folder, exist_ok=True)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(config, f)
+    head, off = {}, 0
+    for name, a in tensors.items():
+        n = int(np.prod(np.shape(a))) * 2
+        head[name] = {"dtype": "BF16", "shape": list(np.shape(a)), "data_offsets": [off, off + n]}
+        off += n
+    hj = json.dumps(head).encode()
+    hj += b" " * (-len(hj) % 8)
+    with open(os.path.join(folder, "model.safetensors"), "wb") as f:
+        f.write(struct.pack("<Q", len(hj)))
+        f.write(hj)
+        for a in tensors.values():
+            f.write(_to_bf16_bits(np.asarray(a)).tobytes())
+
+
+def timerax_tensor_shapes(cfg: dict) -> dict:
+    """name -> shape of every tensor a Timerax config asks for."""
+    W, V = cfg["width"], cfg["vocab"]
+    s = {"embed": (V, W), "final.norm": (W,), "head": (V, W)}
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        s[p + "norm1"] = (W,)
+        if L["type"] == "parallel":
+            a, r = m["left"], m["right"]
+            s[p + "mix.left.q"] = (a["heads"] * a["dim"], W)
+            s[p + "mix.left.k"] = (a["kv_heads"] * a["dim"], W)
+            s[p + "mix.left.v"] = (a["kv_heads"] * a["vdim"], W)
+            s[p + "mix.left.o"] = (W, a["heads"] * a["vdim"])
+            s[p + "mix.right.q"] = (r["heads"] * r["dim"], W)
+            s[p + "mix.right.k"] = (r["heads"] * r["dim"], W)
+            s[p + "mix.right.v"] = (r["heads"] * r["vdim"], W)
+            s[p + "mix.right.g"] = (r["heads"] * r["vdim"], W)
+            s[p + "mix.right.o"] = (W, r["heads"] * r["vdim"])
+            s[p + "mix.right.norm"] = (r["heads"] * r["vdim"],)
+            for g in ("i", "f"):
+                s[p + f"mix.right.{g}"] = (r["heads"], W)
+                s[p + f"mix.right.{g}.b"] = (r["heads"],)
+            s[p + "mix.left.out"] = (W,)
+            s[p + "mix.right.out"] = (W,)
+        else:
+            cq, cv, rk = m["kv_heads"] * m["dim"], m["heads"] * m["vdim"], m.get("rank", max(8, W // 8))
+            s[p + "mix.q"], s[p + "mix.k"], s[p + "mix.v"] = (cq, W), (cq, W), (cv, W)
+            s[p + "mix.q.conv"], s[p + "mix.k.conv"], s[p + "mix.v.conv"] = (cq, m["conv"]), (cq, m["conv"]), (cv, m["conv"])
+            s[p + "mix.b"] = (m["heads"], W)
+            s[p + "mix.A_log"] = (m["heads"],)
+            s[p + "mix.norm"] = (m["vdim"],)
+            s[p + "mix.a1"], s[p + "mix.a2"] = (rk, W), (m["heads"] * m["dim"], rk)
+            s[p + "mix.dt_bias"] = (m["heads"] * m["dim"],)
+            s[p + "mix.g1"], s[p + "mix.g2"] = (rk, W), (cv, rk)
+            s[p + "mix.o"] = (W, cv)
+        f = L.get("mlp")
+        if f:
+            for e in range(f["router"]["experts"]):
+                s[p + f"mlp.e{e}.gate"] = (f["expert"]["ff"], W)
+                s[p + f"mlp.e{e}.up"] = (f["expert"]["ff"], W)
+                s[p + f"mlp.e{e}.down"] = (W, f["expert"]["ff"])
+            s[p + "mlp.router"] = (f["router"]["experts"], W)
+            if f.get("shared"):
+                s[p + "mlp.shared.gate"] = (f["shared"]["ff"], W)
+                s[p + "mlp.shared.up"] = (f["shared"]["ff"], W)
+                s[p + "mlp.shared.down"] = (W, f["shared"]["ff"])
+    return s
+
+
+def random_timerax_tensors(cfg: dict, seed: int = 0) -> dict:
+    """Random weights of a Timerax config: matrices N(0, 1/in), norm weights around zero (layer norms) or around one
+    (plain weights), gate biases and decay parameters in the ranges where the recurrences are neither frozen nor
+    forgetful.  The "rank" key of a channel_delta mixer (the width of its low-rank projections) is read here only."""
+    rng = np.random.default_rng(seed)
+    out = {}
+    for name, shape in timerax_tensor_shapes(cfg).items():
+        last = name.rsplit(".", 1)[-1]
+        if len(shape) == 2 and not name.endswith(".conv"):
+            a = rng.standard_normal(shape) / np.sqrt(shape[1])
+            if name == "embed":
+                a = rng.standard_normal(shape)
+        elif name.endswith(".conv"):
+            a = rng.standard_normal(shape) * 0.5
+        elif last in ("norm1",) or name == "final.norm":
+            a = rng.standard_normal(shape) * 0.1
+        elif name.endswith("f.b"):
+            a = 3.0 + rng.standard_normal(shape)
+        elif name.endswith("i.b"):
+            a = rng.standard_normal(shape) * 0.1
+        elif last == "A_log":
+            a = -1.0 + rng.standard_normal(shape)
+        elif last == "dt_bias":
+            a = -2.0 + rng.standard_normal(shape)
+        else:   # plain weights: .norm, .out
+            a = 1.0 + rng.standard_normal(shape) * 0.1
+        out[name] = a.astype(np.float32)
+    return out

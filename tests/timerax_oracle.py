@@ -151,10 +151,11 @@ def attention_side(h, w, pre, m, eps):
     q = (h @ w[pre + "q"].T).reshape(T, H, D)
     k = (h @ w[pre + "k"].T).reshape(T, G, D)
     v = (h @ w[pre + "v"].T).reshape(T, G, E)
-    cos, sin = rotary_tables(m["rot"], np.arange(T))
-    q, k = rotate_interleaved(q, cos, sin), rotate_interleaved(k, cos, sin)
+    if m.get("rot"):
+        cos, sin = rotary_tables(m["rot"], np.arange(T))
+        q, k = rotate_interleaved(q, cos, sin), rotate_interleaved(k, cos, sin)
     q, k = unit_rms(q, eps), unit_rms(k, eps)
-    o = chunked_attention(q, k, v, float(m["scale"]), int(m["mask"]["size"]))
+    o = chunked_attention(q, k, v, float(m["scale"]), int(m["mask"]["size"]) if m.get("mask") else max(T, 1))
     return o.reshape(T, H * E) @ w[pre + "o"].T
 
 
