@@ -1,0 +1,157 @@
+"""Throughput of a layer-program design beside the llama2 bf16 path at equal size (bench.py --design timerax).
+
+Random weights at sizes that resemble a real model's layers; a few layers only, so that building the folder stays
+short.  For every size: prompt ingestion (one prompt in one step) and batched decoding (one token per live request per
+step, after a prompt each) through ServingEngine.step -- the call a user makes, with the row arrays going up and the
+wanted logits coming back inside the timed region -- and the same two workloads through the llama2 bf16 engine with as
+many layers, the same width, head count and vocabulary, and a dense feed-forward as wide as the experts a token uses.
+With kernels=True the library's per-kernel timeline (THA_TRACE) of one prompt step and one decode step is printed too.
+"""
+from __future__ import annotations
+
+import json
+import os
+import shutil
+import tempfile
+import time
+
+import numpy as np
+
+SIZES = {
+    # width, attention heads / kv heads / head size, block of positions, memory heads, delta heads, experts / top / ff, shared ff
+    "w1024": dict(width=1024, heads=8, kv_heads=2, dim=128, chunk=1024, mheads=4, mdim=64, dheads=8, dkv=4, ddim=64, experts=16, top=2, ff=1024, sff=1024,
+                  vocab=32000, layers=4),
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, chunk=2048, mheads=4, mdim=128, dheads=16, dkv=8, ddim=128, experts=16, top=4, ff=1024, sff=2048,
+                  vocab=32000, layers=4),
+}
+
+
+def timerax_config(s: dict) -> dict:
+    rot = {"base": 500000.0, "dims": s["dim"] // 2, "scaling": {"factor": 8.0, "fast": 32.0, "original": 4096, "slow": 1.0}}
+    left = {"dim": s["dim"], "heads": s["heads"], "kv_heads": s["kv_heads"], "vdim": s["dim"], "mask": {"size": s["chunk"]}, "rot": rot,
+            "scale": s["dim"] ** -0.5}
+    right = {"dim": s["mdim"], "heads": s["mheads"], "vdim": s["mdim"], "gate_cap": 15.0}
+    mlp = {"kind": "moe", "expert": {"ff": s["ff"], "limit": 7.0}, "router": {"experts": s["experts"], "top": s["top"]},
+           "shared": {"ff": s["sff"], "limit": 7.0}}
+    par = {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": mlp}
+    dl = {"type": "channel_delta", "mixer": {"conv": 4, "dim": s["ddim"], "heads": s["dheads"], "kv_heads": s["dkv"], "vdim": s["ddim"], "rank": 64},
+          "mlp": mlp}
+    layers = [dl if i % 4 == 2 else par for i in range(s["layers"])]
+    return {"architecture": "Timerax", "layers": layers, "logit_softcap": 30.0, "norm": {"eps": 1e-5}, "vocab": s["vocab"], "width": s["width"]}
+
+
+def _time_timerax(serving, folder, prompt_len, batch, ctx, steps, warmup, kernels):
+    rng = np.random.default_rng(0)
+    out = {}
+    eng = serving.ServingEngine(folder, "bfloat16", max_tokens=max(prompt_len + 64, batch * (ctx + steps + warmup + 64)), max_seqs=max(batch, 1))
+    vocab = eng.vocab
+    # prompt ingestion: a fresh request per repetition
+    times = []
+    for i in range(warmup + 3):
+        toks = rng.integers(0, vocab, prompt_len).tolist()
+        t0 = time.perf_counter()
+        eng.step([(f"p{i}", toks, [prompt_len - 1])])
+        times.append(time.perf_counter() - t0)
+        eng.finish(f"p{i}")
+    ms = 1e3 * float(np.median(times[warmup:]))
+    out["prefill"] = {"tokens": prompt_len, "ms": ms, "tok_s": prompt_len / ms * 1e3}
+    if kernels:
+        serving.host_lib()   # same process, the CUDA library is loaded: its timeline covers the next step only
+        import ctypes as C
+        cuda = C.CDLL(os.path.join(os.path.dirname(serving.HOST_LIB_PATH), "libtha_b200.so"))
+        cuda.tha_trace_dump(1 << 30)
+        eng.step([("pk", rng.integers(0, vocab, prompt_len).tolist(), [prompt_len - 1])])
+        print(f"# kernels of one prompt step, {prompt_len} tokens", flush=True)
+        cuda.tha_trace_dump(0)
+        eng.finish("pk")
+    # decoding: `batch` requests with `ctx` tokens each, then single tokens
+    ids = [f"d{i}" for i in range(batch)]
+    for i in ids:
+        eng.step([(i, rng.integers(0, vocab, ctx).tolist(), [])])
+    times = []
+    for k in range(warmup + steps):
+        entries = [(i, [int(rng.integers(0, vocab))], [0]) for i in ids]
+        t0 = time.perf_counter()
+        eng.step(entries)
+        times.append(time.perf_counter() - t0)
+    ms = 1e3 * float(np.median(times[warmup:]))
+    out["decode"] = {"batch": batch, "context": ctx, "ms_per_step": ms, "tok_s": batch / ms * 1e3}
+    if kernels:
+        cuda.tha_trace_dump(1 << 30)
+        eng.step([(i, [1], [0]) for i in ids])
+        print(f"# kernels of one decode step, {batch} requests at context {ctx}", flush=True)
+        cuda.tha_trace_dump(0)
+    eng.close()
+    return out
+
+
+def _time_llama(engine_mod, checkpoint_mod, s, prompt_len, batch, ctx, steps, warmup):
+    import torch
+    hidden = s["top"] * s["ff"] + s["sff"]
+    cfg = checkpoint_mod.Config(dim=s["width"], hidden_dim=hidden, n_layers=s["layers"], n_heads=s["heads"], n_kv_heads=s["kv_heads"],
+                                vocab_size=s["vocab"], seq_len=max(prompt_len, ctx + steps + warmup + 8))
+    dw = engine_mod.DeviceWeightsBF16.random(cfg, seed=1, device="cuda")
+    out = {"weights_bytes": dw.nbytes()}
+    e = engine_mod.Engine(dw, max(batch, 1), device="cuda", with_att=False)
+    rng = np.random.default_rng(0)
+    st = torch.cuda.Stream()
+    logits = torch.zeros(1, cfg.vocab_size, device="cuda")
+    with torch.cuda.stream(st):
+        seqs = [(0, 0, rng.integers(3, cfg.vocab_size, size=prompt_len).astype(np.int32))]
+        times = []
+        for _ in range(warmup + 3):
+            st.synchronize()
+            t0 = time.perf_counter()
+            e.prefill(seqs, logits, None, stream=st)
+            logits.cpu()
+            st.synchronize()
+            times.append(time.perf_counter() - t0)
+        ms = 1e3 * float(np.median(times[warmup:]))
+        out["prefill"] = {"tokens": prompt_len, "ms": ms, "tok_s": prompt_len / ms * 1e3}
+        e.prefill([(b, 0, rng.integers(3, cfg.vocab_size, size=ctx).astype(np.int32)) for b in range(batch)], None, None, stream=st)
+        lg = torch.empty(batch, cfg.vocab_size, dtype=torch.float32).pin_memory()
+        times = []
+        for k in range(warmup + steps):
+            tok = rng.integers(3, cfg.vocab_size, size=batch).astype(np.int32)
+            pos = np.full(batch, ctx + k, np.int32)
+            t0 = time.perf_counter()
+            e.forward_batch(tok, pos, lg, stream=st)       # host tokens in, logits back: what the other arm's step does
+            times.append(time.perf_counter() - t0)
+        ms = 1e3 * float(np.median(times[warmup:]))
+        out["decode"] = {"batch": batch, "context": ctx, "ms_per_step": ms, "tok_s": batch / ms * 1e3}
+    return out
+
+
+def timerax_weight_bytes(cfg: dict, shapes: dict) -> dict:
+    total = sum(int(np.prod(sh)) for sh in shapes.values()) * 2
+    active = 0
+    for name, sh in shapes.items():
+        n = int(np.prod(sh)) * 2
+        if ".mlp.e" in name:
+            li = int(name.split(".")[0][1:])
+            r = cfg["layers"][li]["mlp"]["router"]
+            n = n * r["top"] / r["experts"]
+        active += n
+    return {"total": total, "per_token": int(active)}
+
+
+def run(load_pkg, sizes, prompt_len=4096, batch=64, ctx=512, steps=16, warmup=3, kernels=False, llama=True):
+    serving = load_pkg("serving")
+    engine_mod = load_pkg("engine")
+    checkpoint_mod = load_pkg("checkpoint")
+    results = {}
+    for name in sizes:
+        s = SIZES[name]
+        cfg = timerax_config(s)
+        shapes = serving.timerax_tensor_shapes(cfg)
+        tmp = tempfile.mkdtemp(prefix="design_bench_")
+        try:
+            serving.save_model_folder(tmp, cfg, serving.random_timerax_tensors(cfg, 0))
+            r = {"timerax": _time_timerax(serving, tmp, prompt_len, batch, ctx, steps, warmup, kernels)}
+            r["timerax"]["weights_bytes"] = timerax_weight_bytes(cfg, shapes)
+        finally:
+            shutil.rmtree(tmp, ignore_errors=True)
+        if llama:
+            r["llama2_bf16_equal_size"] = _time_llama(engine_mod, checkpoint_mod, s, prompt_len, batch, ctx, steps, warmup)
+        results[name] = r
+    return results

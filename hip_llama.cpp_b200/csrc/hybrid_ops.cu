@@ -8,8 +8,11 @@
 // not depend on how the prompt was cut or on what else is in the step.
 #include <cuda_bf16.h>
 #include <math.h>
+#include <stdlib.h>
+#include <string.h>
 
 #include "common.cuh"
+#include "gemm_tc.h"
 #include "hybrid_ops.cuh"
 #include "tha_hybrid.h"
 
@@ -101,6 +104,113 @@ __global__ void __launch_bounds__(256) hyb_linear_kernel(float* __restrict__ C, 
 }
 
 // ------------------------------------------------------------------------------------------------------------------
+// the same map for bf16 x bf16 on the tensor cores, for the products the TMA-fed matmul of the bf16 path cannot take:
+// rows gathered through an index list and one matrix per group of rows (the experts of a mixture).  64 x 64 tile, k
+// slices of 32 through padded shared memory (global -> registers -> shared, the next slice in flight during the math),
+// 4 warps of 32 x 32, mma.sync m16n8k16 with fp32 accumulators; k ascending, so an output element's sum does not depend
+// on its tile or group.  Needs K % 8 == 0 and 16-byte aligned rows (128-bit loads).
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int MK = 32, MKP = MK + 8;   // padded row: 80 bytes, conflict-free fragment reads
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+__global__ void __launch_bounds__(128) hyb_linear_mma_kernel(float* __restrict__ C, long long ldc, const __nv_bfloat16* __restrict__ A,
+                                                             long long lda, const int* __restrict__ a_rows,
+                                                             const __nv_bfloat16* __restrict__ W, long long w_group_stride, int M, int N,
+                                                             int K, const int* __restrict__ group_off, int n_groups) {
+  __shared__ __align__(16) __nv_bfloat16 As[LT][MKP];
+  __shared__ __align__(16) __nv_bfloat16 Ws[LT][MKP];
+  int g = 0, m0 = 0, m_end = M;
+  if (group_off) {
+    int tile = blockIdx.y, found = 0;
+    for (g = 0; g < n_groups; g++) {
+      const int lo = group_off[g], hi = group_off[g + 1];
+      const int nt = (hi - lo + LT - 1) / LT;
+      if (tile < nt) { m0 = lo + tile * LT; m_end = hi; found = 1; break; }
+      tile -= nt;
+    }
+    if (!found) return;
+  } else {
+    m0 = blockIdx.y * LT;
+    if (m0 >= M) return;
+  }
+  const int n0 = blockIdx.x * LT;
+  const __nv_bfloat16* Wg = W + (size_t)g * w_group_stride;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
+  // loader: 2 chunks of 8 values per thread and matrix; chunk id = threadIdx.x + 128 * u -> row = id / 4, k chunk = id % 4
+  const __nv_bfloat16* a_src[2]; const __nv_bfloat16* w_src[2];
+  int l_row[2], l_kc[2];
+#pragma unroll
+  for (int u = 0; u < 2; u++) {
+    const int id = threadIdx.x + 128 * u;
+    l_row[u] = id >> 2; l_kc[u] = (id & 3) * 8;
+    const int am = m0 + l_row[u];
+    a_src[u] = am < m_end ? A + (size_t)(a_rows ? a_rows[am] : am) * lda : nullptr;
+    const int wr = n0 + l_row[u];
+    w_src[u] = wr < N ? Wg + (size_t)wr * K : nullptr;
+  }
+  uint4 ra[2], rw[2];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int u = 0; u < 2; u++) {
+      const int k = k0 + l_kc[u];
+      ra[u] = (a_src[u] && k < K) ? *reinterpret_cast<const uint4*>(a_src[u] + k) : make_uint4(0, 0, 0, 0);
+      rw[u] = (w_src[u] && k < K) ? *reinterpret_cast<const uint4*>(w_src[u] + k) : make_uint4(0, 0, 0, 0);
+    }
+  };
+  float acc[2][4][4] = {};
+  fetch(0);
+  for (int k0 = 0; k0 < K; k0 += MK) {
+#pragma unroll
+    for (int u = 0; u < 2; u++) {
+      *reinterpret_cast<uint4*>(&As[l_row[u]][l_kc[u]]) = ra[u];
+      *reinterpret_cast<uint4*>(&Ws[l_row[u]][l_kc[u]]) = rw[u];
+    }
+    __syncthreads();
+    if (k0 + MK < K) fetch(k0 + MK);
+#pragma unroll
+    for (int kk = 0; kk < MK; kk += 16) {
+      uint32_t af[2][4], bf[4][2];
+      const int kc = kk + (lane & 3) * 2, rr = lane >> 2;
+#pragma unroll
+      for (int i = 0; i < 2; i++) {
+        const int r = wm + i * 16 + rr;
+        af[i][0] = *reinterpret_cast<const uint32_t*>(&As[r][kc]);
+        af[i][1] = *reinterpret_cast<const uint32_t*>(&As[r + 8][kc]);
+        af[i][2] = *reinterpret_cast<const uint32_t*>(&As[r][kc + 8]);
+        af[i][3] = *reinterpret_cast<const uint32_t*>(&As[r + 8][kc + 8]);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const int n = wn + j * 8 + rr;
+        bf[j][0] = *reinterpret_cast<const uint32_t*>(&Ws[n][kc]);
+        bf[j][1] = *reinterpret_cast<const uint32_t*>(&Ws[n][kc + 8]);
+      }
+#pragma unroll
+      for (int i = 0; i < 2; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) mma_bf16_16816(acc[i][j], af[i], bf[j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++)
+#pragma unroll
+      for (int v = 0; v < 4; v++) {
+        const int m = m0 + wm + i * 16 + (lane >> 2) + (v >> 1) * 8;
+        const int n = n0 + wn + j * 8 + (lane & 3) * 2 + (v & 1);
+        if (m < m_end && n < N) C[(size_t)m * ldc + n] = acc[i][j][v];
+      }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
 // rotary tables: float64 angles so that position * frequency keeps its low bits at long contexts
 // ------------------------------------------------------------------------------------------------------------------
 __global__ void hyb_rotary_kernel(const double* __restrict__ inv_freq, int half, float mag, const int* __restrict__ pos, int n_rows,
@@ -169,53 +279,135 @@ __global__ void hyb_attn_prepare_kernel(tha_attn_t a, tha_rows_t rows, tha_kv_t 
 }
 
 // ------------------------------------------------------------------------------------------------------------------
-// attention: one block per (row, head).  Scores of the visible keys into shared memory (a warp per key, lanes over the
-// head's dimensions), softmax, then the weighted sum of the value rows (threads over value channels x key parts).
-// Visible keys: first .. pos with first = the start of pos's block of `chunk` positions (0 when chunk == 0).
+// attention, prompts and decoding alike.  A block takes 16 (position, query head) pairs that share one key/value head:
+// AP consecutive positions of one sequence x AG heads of the group (AG = min(group size, 16), AP = 16 / AG), so a key
+// tile is read once for all of them.  Keys come in tiles of 32 aligned to absolute multiples of 32: whatever the step's
+// cut, a position meets the same tiles in the same order and its running (max, sum, accumulator) takes the same values.
+// Per tile: scores (warp = 4 pairs, lane = key), masked to the query's visible range [start of its block of `chunk`
+// positions, own position], online softmax per pair, then P.V with lanes over value channels.
 // ------------------------------------------------------------------------------------------------------------------
+constexpr int ATT_PAIRS = 16, ATT_KEYS = 32, ATT_MAX_VC = 8;   // value channels per lane: vdim <= 256
+
 template <typename T>
-__global__ void hyb_attn_kernel(tha_attn_t a, tha_rows_t rows, tha_kv_t kv, const float* __restrict__ q, T* __restrict__ out) {
+__global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t rows, tha_kv_t kv, const float* __restrict__ q,
+                                                       T* __restrict__ out, int AG, int AP) {
   extern __shared__ float sm[];
-  __shared__ float red[33];
-  const int r = blockIdx.x, h = blockIdx.y;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  const int slot = rows.seq_slot[rows.row_seq[r]], t = rows.pos[r];
-  const int first = a.chunk > 0 ? (t / a.chunk) * a.chunk : 0;
-  const int nk = t - first + 1;
-  const int g = h / (a.heads / a.kv_heads);
-  float* sq = sm;                 // [dim]
-  float* sc = sm + a.dim;         // [nk]
-  float* part = sc + nk;          // [parts * vdim]
-  for (int i = threadIdx.x; i < a.dim; i += blockDim.x) sq[i] = q[(size_t)r * a.heads * a.dim + (size_t)h * a.dim + i];
-  __syncthreads();
-  float mx = -INFINITY;
-  for (int j = warp; j < nk; j += nwarps) {
-    const float* kr = kv.k_pool + hyb_kv_row(kv, slot, first + j, a.cache_layer) + (size_t)g * a.dim;
-    float s = 0.f;
-    for (int i = lane; i < a.dim; i += 32) s = fmaf(sq[i], kr[i], s);
-    s = warp_sum(s) * a.scale;
-    if (lane == 0) sc[j] = s;
-    mx = fmaxf(mx, s);
+  const int D = a.dim, E = a.vdim, gsize = a.heads / a.kv_heads;
+  float* Qs = sm;                              // [16][D]
+  float* Ks = Qs + ATT_PAIRS * D;              // [32][D + 1]
+  float* Vs = Ks + ATT_KEYS * (D + 1);         // [32][E]
+  float* Ps = Vs + ATT_KEYS * E;               // [16][32]
+  // which sequence and which positions: tiles of AP rows per sequence, found by walking the sequences
+  int seq = -1, r0 = 0, r_end = 0;
+  {
+    int tile = blockIdx.x;
+    for (int s = 0; s < rows.n_seqs; s++) {
+      const int lo = rows.seq_first[s], hi = rows.seq_first[s + 1];
+      const int nt = (hi - lo + AP - 1) / AP;
+      if (tile < nt) { seq = s; r0 = lo + tile * AP; r_end = min(hi, r0 + AP); break; }
+      tile -= nt;
+    }
+    if (seq < 0) return;
   }
-  mx = block_max(mx, red);
-  float sum = 0.f;
-  for (int j = threadIdx.x; j < nk; j += blockDim.x) { const float p = expf(sc[j] - mx); sc[j] = p; sum += p; }
-  sum = block_sum(sum, red);
-  const float inv = 1.0f / sum;
-  // weighted values: thread (part, e) sums keys part, part + parts, ...
-  const int parts = max(1, (int)blockDim.x / a.vdim);
-  for (int idx = threadIdx.x; idx < parts * a.vdim; idx += blockDim.x) {
-    const int p = idx / a.vdim, e = idx % a.vdim;
-    float acc = 0.f;
-    for (int j = p; j < nk; j += parts)
-      acc = fmaf(sc[j], kv.v_pool[hyb_kv_row(kv, slot, first + j, a.cache_layer) + (size_t)g * a.vdim + e], acc);
-    part[idx] = acc;
+  const int g = blockIdx.y, part = blockIdx.z;
+  const int slot = rows.seq_slot[seq];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int p_first = rows.pos[r0], p_last = p_first + (r_end - r0) - 1;
+  // the block's pairs
+  for (int i = threadIdx.x; i < ATT_PAIRS * D; i += blockDim.x) {
+    const int pr = i / D, d = i - pr * D;
+    const int r = r0 + pr / AG, hg = part * AG + pr % AG;
+    Qs[i] = (r < r_end && hg < gsize) ? q[(size_t)r * a.heads * D + (size_t)(g * gsize + hg) * D + d] : 0.f;
   }
-  __syncthreads();
-  for (int e = threadIdx.x; e < a.vdim; e += blockDim.x) {
-    float acc = 0.f;
-    for (int p = 0; p < parts; p++) acc += part[p * a.vdim + e];
-    hyb_store(out + (size_t)r * a.heads * a.vdim + (size_t)h * a.vdim + e, acc * inv);
+  int my_pos[4], my_first[4];
+  bool my_ok[4];
+  float m_run[4], l_run[4], acc[4][ATT_MAX_VC];
+#pragma unroll
+  for (int rr = 0; rr < 4; rr++) {
+    const int pr = warp * 4 + rr;
+    const int r = r0 + pr / AG, hg = part * AG + pr % AG;
+    my_ok[rr] = r < r_end && hg < gsize;
+    my_pos[rr] = p_first + pr / AG;
+    my_first[rr] = a.chunk > 0 ? (my_pos[rr] / a.chunk) * a.chunk : 0;
+    m_run[rr] = -INFINITY; l_run[rr] = 0.f;
+#pragma unroll
+    for (int c = 0; c < ATT_MAX_VC; c++) acc[rr][c] = 0.f;
+  }
+  const int key_lo = a.chunk > 0 ? (p_first / a.chunk) * a.chunk : 0;
+  for (int kt = (key_lo / ATT_KEYS) * ATT_KEYS; kt <= p_last; kt += ATT_KEYS) {
+    __syncthreads();   // the previous tile is consumed (and Qs is written, the first time)
+    // a warp fetches 8 keys: all 8 table entries first, then the rows, so that the loads are in flight together
+    size_t krow[ATT_KEYS / 4];
+#pragma unroll
+    for (int jj = 0; jj < ATT_KEYS / 4; jj++) {
+      const int t = kt + warp + 4 * jj;
+      krow[jj] = (t <= p_last && t >= key_lo) ? hyb_kv_row(kv, slot, t, a.cache_layer) : (size_t)-1;
+    }
+#pragma unroll
+    for (int jj = 0; jj < ATT_KEYS / 4; jj++) {
+      const int j = warp + 4 * jj;
+      const bool live = krow[jj] != (size_t)-1;
+      const float* kr = kv.k_pool + (live ? krow[jj] : 0) + (size_t)g * D;
+      const float* vr = kv.v_pool + (live ? krow[jj] : 0) + (size_t)g * E;
+      for (int d = lane; d < D; d += 32) Ks[j * (D + 1) + d] = live ? kr[d] : 0.f;
+      for (int e = lane; e < E; e += 32) Vs[j * E + e] = live ? vr[e] : 0.f;
+    }
+    __syncthreads();
+    float sc[4] = {0.f, 0.f, 0.f, 0.f};
+    const float* kl = Ks + lane * (D + 1);
+    const float* q0 = Qs + (warp * 4) * D;
+    for (int d = 0; d < D; d++) {
+      const float kd = kl[d];
+      sc[0] = fmaf(q0[d], kd, sc[0]);
+      sc[1] = fmaf(q0[D + d], kd, sc[1]);
+      sc[2] = fmaf(q0[2 * D + d], kd, sc[2]);
+      sc[3] = fmaf(q0[3 * D + d], kd, sc[3]);
+    }
+    const int t = kt + lane;
+#pragma unroll
+    for (int rr = 0; rr < 4; rr++) {
+      const bool vis = my_ok[rr] && t <= my_pos[rr] && t >= my_first[rr];
+      const float sv = vis ? sc[rr] * a.scale : -INFINITY;
+      const float m_new = fmaxf(m_run[rr], warp_max(sv));
+      float p = 0.f, corr = 1.f;
+      if (m_new > -INFINITY) {
+        p = vis ? expf(sv - m_new) : 0.f;
+        corr = expf(m_run[rr] - m_new);      // 0 when nothing was seen before
+      }
+      l_run[rr] = l_run[rr] * corr + warp_sum(p);
+      m_run[rr] = m_new;
+      Ps[(warp * 4 + rr) * ATT_KEYS + lane] = p;
+#pragma unroll
+      for (int c = 0; c < ATT_MAX_VC; c++) acc[rr][c] *= corr;
+    }
+    __syncwarp();
+    const float* pw = Ps + (warp * 4) * ATT_KEYS;
+    for (int j = 0; j < ATT_KEYS; j++) {
+      const float p0 = pw[j], p1 = pw[ATT_KEYS + j], p2 = pw[2 * ATT_KEYS + j], p3 = pw[3 * ATT_KEYS + j];
+#pragma unroll
+      for (int c = 0; c < ATT_MAX_VC; c++) {
+        const int e = lane + 32 * c;
+        if (e < E) {
+          const float v = Vs[j * E + e];
+          acc[0][c] = fmaf(p0, v, acc[0][c]);
+          acc[1][c] = fmaf(p1, v, acc[1][c]);
+          acc[2][c] = fmaf(p2, v, acc[2][c]);
+          acc[3][c] = fmaf(p3, v, acc[3][c]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int rr = 0; rr < 4; rr++) {
+    if (!my_ok[rr]) continue;
+    const int pr = warp * 4 + rr;
+    const int r = r0 + pr / AG, h = g * gsize + part * AG + pr % AG;
+    const float inv = 1.0f / l_run[rr];
+#pragma unroll
+    for (int c = 0; c < ATT_MAX_VC; c++) {
+      const int e = lane + 32 * c;
+      if (e < E) hyb_store(out + (size_t)r * a.heads * E + (size_t)h * E + e, acc[rr][c] * inv);
+    }
   }
 }
 
@@ -227,64 +419,280 @@ __device__ __forceinline__ float hyb_logsigmoid(float z) { return fminf(z, 0.f) 
 __device__ __forceinline__ float hyb_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float hyb_softplus(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
 
-template <typename T>
-__global__ void hyb_mem_scan_kernel(tha_mem_t m, tha_rows_t rows, tha_state_store_t st, const float* __restrict__ proj, long long ldp,
-                                    T* __restrict__ out) {
+// The state's value columns are independent of each other (column e of S only ever meets v[e]), so a head is cut into
+// slices of SC columns, one block each: block (sequence, head, slice) keeps S[:, slice] in shared memory, its own copy of
+// n and m, and walks the sequence's rows in order.  Thread (part, e) owns the rows d = part, part + parts, ... of column e:
+// it updates them and accumulates its share of S^T q in the same pass.  The inputs of the next token are fetched while
+// the current one is computed, and live in alternating buffers: two barriers per token.
+// Output: o / max(|n.q|, exp(-m)) per (row, head, column) in fp32; the head norm and the output gate follow in
+// hyb_head_gate_kernel, which needs all columns of a head.
+constexpr int SCAN_THREADS = 256;
+
+__global__ void __launch_bounds__(SCAN_THREADS) hyb_mem_scan_kernel(tha_mem_t m, tha_rows_t rows, tha_state_store_t st,
+                                                                    const float* __restrict__ proj, long long ldp, float* __restrict__ o_raw, int SC) {
   extern __shared__ float sm[];
-  __shared__ float red[33];
-  const int s = blockIdx.x, h = blockIdx.y;
-  const int D = m.dim, E = m.vdim, nt = blockDim.x;
-  float* S = sm;              // [D * E]
-  float* nv = S + D * E;      // [D]
-  float* sq = nv + D;         // [D]
-  float* sk = sq + D;         // [D]
-  float* sv = sk + D;         // [E]
-  const int parts = max(1, nt / E);
-  float* part = sv + E;       // [parts * E]
-  float* gstate = st.base + (size_t)rows.seq_slot[s] * st.slot_floats + m.state_off + (size_t)h * (D * E + D + 1);
-  for (int i = threadIdx.x; i < D * E + D; i += nt) S[i] = gstate[i];   // S then n, adjacent in both places
-  float mrun = gstate[D * E + D];
-  __syncthreads();
+  const int s = blockIdx.x, h = blockIdx.y, e0 = blockIdx.z * SC;
+  const int D = m.dim, E = m.vdim, nt = SCAN_THREADS;
+  const int ec = min(SC, E - e0);
+  const int parts = nt / SC;
+  float* S = sm;                    // [D][SC]
+  float* nv = S + D * SC;           // [D]
+  float* in = nv + D;               // 2 x (q [D] | k [D] | v [SC] | ig | fg)
+  const int in_stride = 2 * D + SC + 2;
+  float* part = in + 2 * in_stride; // [parts][SC]
+  float* gstate = st.base + (size_t)rows.seq_slot[s] * st.slot_floats + m.state_off + (size_t)h * ((size_t)D * E + D + 1);
+  for (int i = threadIdx.x; i < D * SC; i += nt) { const int d = i / SC, e = i - d * SC; S[i] = e < ec ? gstate[(size_t)d * E + e0 + e] : 0.f; }
+  for (int i = threadIdx.x; i < D; i += nt) nv[i] = gstate[(size_t)D * E + i];
+  float mrun = gstate[(size_t)D * E + D];
   const float qscale = 1.0f / sqrtf((float)D);
-  for (int r = rows.seq_first[s]; r < rows.seq_first[s + 1]; r++) {
+  const int r_begin = rows.seq_first[s], r_end = rows.seq_first[s + 1];
+  // element i of a token's inputs: q, k, v slice, the two raw gates
+  auto fetch = [&](int r, int i) -> float {
     const float* pr = proj + (size_t)r * ldp;
-    for (int i = threadIdx.x; i < D; i += nt) { sq[i] = pr[m.o_q + h * D + i] * qscale; sk[i] = pr[m.o_k + h * D + i]; }
-    for (int i = threadIdx.x; i < E; i += nt) sv[i] = pr[m.o_v + h * E + i];
-    const float ig = hyb_softcap(pr[m.o_i + h] + m.b_i[h], m.gate_cap);
-    const float fg = hyb_logsigmoid(hyb_softcap(pr[m.o_f + h] + m.b_f[h], m.gate_cap));
+    if (i < D) return pr[m.o_q + h * D + i] * qscale;
+    if (i < 2 * D) return pr[m.o_k + h * D + (i - D)];
+    if (i < 2 * D + SC) return (i - 2 * D) < ec ? pr[m.o_v + h * E + e0 + (i - 2 * D)] : 0.f;
+    return i == 2 * D + SC ? pr[m.o_i + h] + m.b_i[h] : pr[m.o_f + h] + m.b_f[h];
+  };
+  constexpr int PF = 4;             // prefetch registers per thread: up to 1024 inputs per token
+  float pf[PF];
+#pragma unroll
+  for (int u = 0; u < PF; u++) { const int i = threadIdx.x + u * nt; pf[u] = (i < in_stride && r_begin < r_end) ? fetch(r_begin, i) : 0.f; }
+  const int pe = threadIdx.x % SC, pp = threadIdx.x / SC;
+  for (int r = r_begin; r < r_end; r++) {
+    float* cur = in + ((r - r_begin) & 1) * in_stride;
+#pragma unroll
+    for (int u = 0; u < PF; u++) { const int i = threadIdx.x + u * nt; if (i < in_stride) cur[i] = pf[u]; }
+    for (int i = threadIdx.x + PF * nt; i < in_stride; i += nt) cur[i] = fetch(r, i);   // very wide heads: the rest, unprefetched
+    if (r + 1 < r_end) {
+#pragma unroll
+      for (int u = 0; u < PF; u++) { const int i = threadIdx.x + u * nt; if (i < in_stride) pf[u] = fetch(r + 1, i); }
+    }
+    __syncthreads();
+    const float* sq = cur; const float* sk = cur + D; const float* sv = cur + 2 * D;
+    const float ig = hyb_softcap(cur[2 * D + SC], m.gate_cap);
+    const float fg = hyb_logsigmoid(hyb_softcap(cur[2 * D + SC + 1], m.gate_cap));
     const float mnew = fmaxf(fg + mrun, ig);
     const float a = expf(fg + mrun - mnew), b = expf(ig - mnew);
     mrun = mnew;
-    __syncthreads();
-    for (int i = threadIdx.x; i < D * E; i += nt) { const int d = i / E, e = i - d * E; S[i] = fmaf(a, S[i], b * sk[d] * sv[e]); }
+    if (pp < parts) {
+      const float bv = b * sv[pe];
+      float acc = 0.f;
+      for (int d = pp; d < D; d += parts) { const float v = fmaf(a, S[d * SC + pe], sk[d] * bv); S[d * SC + pe] = v; acc = fmaf(v, sq[d], acc); }
+      part[pp * SC + pe] = acc;
+    }
     for (int i = threadIdx.x; i < D; i += nt) nv[i] = fmaf(a, nv[i], b * sk[i]);
     __syncthreads();
-    for (int idx = threadIdx.x; idx < parts * E; idx += nt) {
-      const int p = idx / E, e = idx - p * E;
-      float acc = 0.f;
-      for (int d = p; d < D; d += parts) acc = fmaf(S[d * E + e], sq[d], acc);
-      part[idx] = acc;
+    if (threadIdx.x < 32) {          // one warp finishes the token: n.q, the column sums, the division
+      float nq = 0.f;
+      for (int i = threadIdx.x; i < D; i += 32) nq = fmaf(nv[i], sq[i], nq);
+      nq = warp_sum(nq);
+      const float den = fmaxf(fabsf(nq), expf(-mrun)) + 1e-6f;
+      for (int e = threadIdx.x; e < ec; e += 32) {
+        float acc = 0.f;
+        for (int p = 0; p < parts; p++) acc += part[p * SC + e];
+        o_raw[(size_t)r * m.heads * E + (size_t)h * E + e0 + e] = acc / den;
+      }
     }
-    float nq = 0.f;
-    for (int i = threadIdx.x; i < D; i += nt) nq = fmaf(nv[i], sq[i], nq);
-    nq = block_sum(nq, red);   // also orders `part`
-    const float den = fmaxf(fabsf(nq), expf(-mrun)) + 1e-6f;
-    float ss = 0.f;
-    for (int e = threadIdx.x; e < E; e += nt) {
-      float acc = 0.f;
-      for (int p = 0; p < parts; p++) acc += part[p * E + e];
-      acc /= den;
-      sv[e] = acc;            // sv is free again (its last reader was the S update, two barriers back)
-      ss = fmaf(acc, acc, ss);
-    }
-    ss = block_sum(ss, red);
-    const float inv = 1.0f / sqrtf(ss / (float)E + m.eps);
-    for (int e = threadIdx.x; e < E; e += nt)
-      hyb_store(out + (size_t)r * m.heads * E + (size_t)h * E + e, sv[e] * inv * m.norm[h * E + e] * hyb_sigmoid(pr[m.o_g + h * E + e]));
-    __syncthreads();
+    // no barrier here: the next token writes the other input buffer, and `part` is rewritten only after its barrier
   }
-  for (int i = threadIdx.x; i < D * E + D; i += nt) gstate[i] = S[i];
-  if (threadIdx.x == 0) gstate[D * E + D] = mrun;
+  __syncthreads();
+  for (int i = threadIdx.x; i < D * SC; i += nt) { const int d = i / SC, e = i - d * SC; if (e < ec) gstate[(size_t)d * E + e0 + e] = S[i]; }
+  if (blockIdx.z == 0) {
+    for (int i = threadIdx.x; i < D; i += nt) gstate[(size_t)D * E + i] = nv[i];
+    if (threadIdx.x == 0) gstate[(size_t)D * E + D] = mrun;
+  }
+}
+
+// The same two recurrences with the state in REGISTERS, for head sizes up to 256 key channels: a warp owns SCW value
+// columns, lane l the key channels l, l + 32, ... of those columns.  Nothing is shared between warps, so a token costs no
+// block barrier: the column sums S^T q (and S^T k) are warp shuffles, the next token's inputs are fetched a token ahead.
+constexpr int SCW = 2, SCAN_WARPS = 4;
+
+template <int RPL>
+__global__ void __launch_bounds__(32 * SCAN_WARPS) hyb_mem_scan_warp_kernel(tha_mem_t m, tha_rows_t rows, tha_state_store_t st,
+                                                                            const float* __restrict__ proj, long long ldp,
+                                                                            float* __restrict__ o_raw) {
+  const int s = blockIdx.x, h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int D = m.dim, E = m.vdim;
+  const int e0 = (blockIdx.z * SCAN_WARPS + warp) * SCW;
+  if (e0 >= E) return;
+  float* gstate = st.base + (size_t)rows.seq_slot[s] * st.slot_floats + m.state_off + (size_t)h * ((size_t)D * E + D + 1);
+  float S[RPL][SCW], nv[RPL];
+#pragma unroll
+  for (int i = 0; i < RPL; i++) {
+    const int d = lane + 32 * i;
+    nv[i] = d < D ? gstate[(size_t)D * E + d] : 0.f;
+#pragma unroll
+    for (int c = 0; c < SCW; c++) S[i][c] = (d < D && e0 + c < E) ? gstate[(size_t)d * E + e0 + c] : 0.f;
+  }
+  float mrun = gstate[(size_t)D * E + D];
+  const float qscale = 1.0f / sqrtf((float)D);
+  const int r_begin = rows.seq_first[s], r_end = rows.seq_first[s + 1];
+  float q[RPL], k[RPL], v[SCW], gi = 0.f, gf = 0.f;
+  auto fetch = [&](int r) {
+    const float* pr = proj + (size_t)r * ldp;
+#pragma unroll
+    for (int i = 0; i < RPL; i++) {
+      const int d = lane + 32 * i;
+      q[i] = d < D ? pr[m.o_q + h * D + d] : 0.f;
+      k[i] = d < D ? pr[m.o_k + h * D + d] : 0.f;
+    }
+#pragma unroll
+    for (int c = 0; c < SCW; c++) v[c] = e0 + c < E ? pr[m.o_v + h * E + e0 + c] : 0.f;
+    gi = pr[m.o_i + h];
+    gf = pr[m.o_f + h];
+  };
+  if (r_begin < r_end) fetch(r_begin);
+  const float bi = m.b_i[h], bf = m.b_f[h];
+  for (int r = r_begin; r < r_end; r++) {
+    float cq[RPL], ck[RPL], cv[SCW];
+#pragma unroll
+    for (int i = 0; i < RPL; i++) { cq[i] = q[i] * qscale; ck[i] = k[i]; }
+#pragma unroll
+    for (int c = 0; c < SCW; c++) cv[c] = v[c];
+    const float ig = hyb_softcap(gi + bi, m.gate_cap);
+    const float fg = hyb_logsigmoid(hyb_softcap(gf + bf, m.gate_cap));
+    if (r + 1 < r_end) fetch(r + 1);
+    const float mnew = fmaxf(fg + mrun, ig);
+    const float a = expf(fg + mrun - mnew), b = expf(ig - mnew);
+    mrun = mnew;
+    float nq = 0.f, acc[SCW];
+#pragma unroll
+    for (int c = 0; c < SCW; c++) acc[c] = 0.f;
+#pragma unroll
+    for (int i = 0; i < RPL; i++) {
+      nv[i] = fmaf(a, nv[i], b * ck[i]);
+      nq = fmaf(nv[i], cq[i], nq);
+#pragma unroll
+      for (int c = 0; c < SCW; c++) {
+        S[i][c] = fmaf(a, S[i][c], ck[i] * (b * cv[c]));
+        acc[c] = fmaf(S[i][c], cq[i], acc[c]);
+      }
+    }
+    nq = warp_sum(nq);
+    const float den = fmaxf(fabsf(nq), expf(-mrun)) + 1e-6f;
+#pragma unroll
+    for (int c = 0; c < SCW; c++) {
+      const float o = warp_sum(acc[c]);
+      if (lane == c && e0 + c < E) o_raw[(size_t)r * m.heads * E + (size_t)h * E + e0 + c] = o / den;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < RPL; i++) {
+    const int d = lane + 32 * i;
+    if (d >= D) continue;
+#pragma unroll
+    for (int c = 0; c < SCW; c++)
+      if (e0 + c < E) gstate[(size_t)d * E + e0 + c] = S[i][c];
+    if (e0 == 0) gstate[(size_t)D * E + d] = nv[i];
+  }
+  if (e0 == 0 && lane == 0) gstate[(size_t)D * E + D] = mrun;
+}
+
+template <int RPL>
+__global__ void __launch_bounds__(32 * SCAN_WARPS) hyb_delta_scan_warp_kernel(tha_delta_t dl, tha_rows_t rows, tha_state_store_t st,
+                                                                              const float* __restrict__ qkv, const float* __restrict__ proj,
+                                                                              long long ldp, const float* __restrict__ dt_raw,
+                                                                              float* __restrict__ o_raw) {
+  const int s = blockIdx.x, h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int D = dl.dim, E = dl.vdim;
+  const int e0 = (blockIdx.z * SCAN_WARPS + warp) * SCW;
+  if (e0 >= E) return;
+  const int hk = h / (dl.heads / dl.kv_heads);
+  const int C = 2 * dl.kv_heads * D + dl.heads * E;
+  float* gstate = st.base + (size_t)rows.seq_slot[s] * st.slot_floats + dl.state_off + (size_t)h * D * E;
+  float S[RPL][SCW], bias[RPL];
+#pragma unroll
+  for (int i = 0; i < RPL; i++) {
+    const int d = lane + 32 * i;
+    bias[i] = d < D ? dl.dt_bias[h * D + d] : 0.f;
+#pragma unroll
+    for (int c = 0; c < SCW; c++) S[i][c] = (d < D && e0 + c < E) ? gstate[(size_t)d * E + e0 + c] : 0.f;
+  }
+  const float decay_rate = expf(dl.a_log[h]);
+  const float qscale = 1.0f / sqrtf((float)D);
+  const int r_begin = rows.seq_first[s], r_end = rows.seq_first[s + 1];
+  float q[RPL], k[RPL], dt[RPL], v[SCW], braw = 0.f;
+  auto fetch = [&](int r) {
+    const float* x = qkv + (size_t)r * C;
+#pragma unroll
+    for (int i = 0; i < RPL; i++) {
+      const int d = lane + 32 * i;
+      q[i] = d < D ? x[hk * D + d] : 0.f;
+      k[i] = d < D ? x[dl.kv_heads * D + hk * D + d] : 0.f;
+      dt[i] = d < D ? dt_raw[(size_t)r * dl.heads * D + h * D + d] : 0.f;
+    }
+#pragma unroll
+    for (int c = 0; c < SCW; c++) v[c] = e0 + c < E ? x[2 * dl.kv_heads * D + h * E + e0 + c] : 0.f;
+    braw = proj[(size_t)r * ldp + dl.o_b + h];
+  };
+  if (r_begin < r_end) fetch(r_begin);
+  for (int r = r_begin; r < r_end; r++) {
+    float cq[RPL], ck[RPL], cg[RPL], cv[SCW];
+    float qq = 0.f, kk = 0.f;
+#pragma unroll
+    for (int i = 0; i < RPL; i++) {
+      cq[i] = q[i]; ck[i] = k[i];
+      qq = fmaf(cq[i], cq[i], qq);
+      kk = fmaf(ck[i], ck[i], kk);
+      cg[i] = expf(-decay_rate * hyb_softplus(dt[i] + bias[i]));   // lanes past D hold S = 0, whatever their decay
+    }
+#pragma unroll
+    for (int c = 0; c < SCW; c++) cv[c] = v[c];
+    const float beta = hyb_sigmoid(braw);
+    if (r + 1 < r_end) fetch(r + 1);
+    qq = warp_sum(qq);
+    kk = warp_sum(kk);
+    const float qn = qscale / sqrtf(qq + 1e-6f), kn = 1.0f / sqrtf(kk + 1e-6f);
+    float kv[SCW], o[SCW];
+#pragma unroll
+    for (int c = 0; c < SCW; c++) { kv[c] = 0.f; o[c] = 0.f; }
+#pragma unroll
+    for (int i = 0; i < RPL; i++) {
+      ck[i] *= kn;
+      cq[i] *= qn;
+#pragma unroll
+      for (int c = 0; c < SCW; c++) { S[i][c] *= cg[i]; kv[c] = fmaf(S[i][c], ck[i], kv[c]); }
+    }
+    float u[SCW];
+#pragma unroll
+    for (int c = 0; c < SCW; c++) u[c] = beta * (cv[c] - warp_sum(kv[c]));
+#pragma unroll
+    for (int i = 0; i < RPL; i++)
+#pragma unroll
+      for (int c = 0; c < SCW; c++) { S[i][c] = fmaf(ck[i], u[c], S[i][c]); o[c] = fmaf(S[i][c], cq[i], o[c]); }
+#pragma unroll
+    for (int c = 0; c < SCW; c++) {
+      const float ov = warp_sum(o[c]);
+      if (lane == c && e0 + c < E) o_raw[(size_t)r * dl.heads * E + (size_t)h * E + e0 + c] = ov;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < RPL; i++) {
+    const int d = lane + 32 * i;
+    if (d >= D) continue;
+#pragma unroll
+    for (int c = 0; c < SCW; c++)
+      if (e0 + c < E) gstate[(size_t)d * E + e0 + c] = S[i][c];
+  }
+}
+
+// out = o / rms(o over the head) * norm * sigmoid(gate), dtype-typed; a warp per (row, head)
+template <typename T>
+__global__ void hyb_head_gate_kernel(T* __restrict__ out, const float* __restrict__ o_raw, int n_rows, int heads, int E, float eps,
+                                     const float* __restrict__ norm, int norm_per_head, const float* __restrict__ gate, long long ldg) {
+  const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (idx >= n_rows * heads) return;
+  const int r = idx / heads, h = idx - r * heads;
+  const float* o = o_raw + (size_t)r * heads * E + (size_t)h * E;
+  float ss = 0.f;
+  for (int e = lane; e < E; e += 32) ss = fmaf(o[e], o[e], ss);
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)E + eps);
+  for (int e = lane; e < E; e += 32)
+    hyb_store(out + (size_t)r * heads * E + (size_t)h * E + e,
+              o[e] * inv * norm[norm_per_head ? h * E + e : e] * hyb_sigmoid(gate[(size_t)r * ldg + h * E + e]));
 }
 
 // ------------------------------------------------------------------------------------------------------------------
@@ -319,83 +727,87 @@ __global__ void hyb_conv_tail_kernel(tha_rows_t rows, tha_state_store_t st, long
 }
 
 // ------------------------------------------------------------------------------------------------------------------
-// gated delta rule: one block per (sequence, value head); S [dim, vdim] in shared memory.  A thread (part, e) owns the
-// rows d = part, part + parts, ... of column e: decay, read S^T k, write k u^T and read S^T q without leaving its column.
+// gated delta rule: block (sequence, value head, column slice) as in the matrix memory.  Per token, thread (part, e):
+// decay its rows of column e and sum S^T k; after the column's u = beta (v - S^T k) is known, add k u and sum S^T q.
+// Output: S^T q per (row, head, column) in fp32 (norm and gate in hyb_head_gate_kernel).
 // ------------------------------------------------------------------------------------------------------------------
-template <typename T>
-__global__ void hyb_delta_scan_kernel(tha_delta_t dl, tha_rows_t rows, tha_state_store_t st, const float* __restrict__ qkv,
-                                      const float* __restrict__ proj, long long ldp, const float* __restrict__ dt_raw,
-                                      const float* __restrict__ gate_raw, T* __restrict__ out) {
+__global__ void __launch_bounds__(SCAN_THREADS) hyb_delta_scan_kernel(tha_delta_t dl, tha_rows_t rows, tha_state_store_t st,
+                                                                      const float* __restrict__ qkv, const float* __restrict__ proj, long long ldp,
+                                                                      const float* __restrict__ dt_raw, float* __restrict__ o_raw, int SC) {
   extern __shared__ float sm[];
-  __shared__ float red[33];
-  const int s = blockIdx.x, h = blockIdx.y;
-  const int D = dl.dim, E = dl.vdim, nt = blockDim.x;
+  const int s = blockIdx.x, h = blockIdx.y, e0 = blockIdx.z * SC;
+  const int D = dl.dim, E = dl.vdim, nt = SCAN_THREADS;
+  const int ec = min(SC, E - e0);
   const int hk = h / (dl.heads / dl.kv_heads);
   const int C = 2 * dl.kv_heads * D + dl.heads * E;
-  const int parts = max(1, nt / E);
-  float* S = sm;               // [D * E]
-  float* sq = S + D * E;       // [D]
-  float* sk = sq + D;          // [D]
-  float* sg = sk + D;          // [D]
-  float* su = sg + D;          // [E]
-  float* part = su + E;        // [parts * E]
+  const int parts = nt / SC;
+  float* S = sm;                     // [D][SC]
+  float* in = S + D * SC;            // 2 x (q [D] | k [D] | g [D] | v [SC] | beta)
+  const int in_stride = 3 * D + SC + 1;
+  float* part = in + 2 * in_stride;  // [parts][SC]
+  float* su = part + parts * SC;     // [SC]
   float* gstate = st.base + (size_t)rows.seq_slot[s] * st.slot_floats + dl.state_off + (size_t)h * D * E;
-  for (int i = threadIdx.x; i < D * E; i += nt) S[i] = gstate[i];
+  for (int i = threadIdx.x; i < D * SC; i += nt) { const int d = i / SC, e = i - d * SC; S[i] = e < ec ? gstate[(size_t)d * E + e0 + e] : 0.f; }
   const float decay_rate = expf(dl.a_log[h]);
   const float qscale = 1.0f / sqrtf((float)D);
-  __syncthreads();
-  for (int r = rows.seq_first[s]; r < rows.seq_first[s + 1]; r++) {
+  const int r_begin = rows.seq_first[s], r_end = rows.seq_first[s + 1];
+  auto fetch = [&](int r, int i) -> float {
     const float* x = qkv + (size_t)r * C;
+    if (i < D) return x[hk * D + i];
+    if (i < 2 * D) return x[dl.kv_heads * D + hk * D + (i - D)];
+    if (i < 3 * D) { const int d = i - 2 * D; return expf(-decay_rate * hyb_softplus(dt_raw[(size_t)r * dl.heads * D + h * D + d] + dl.dt_bias[h * D + d])); }
+    if (i < 3 * D + SC) return (i - 3 * D) < ec ? x[2 * dl.kv_heads * D + h * E + e0 + (i - 3 * D)] : 0.f;
+    return hyb_sigmoid(proj[(size_t)r * ldp + dl.o_b + h]);
+  };
+  constexpr int PF = 4;
+  float pf[PF];
+#pragma unroll
+  for (int u = 0; u < PF; u++) { const int i = threadIdx.x + u * nt; pf[u] = (i < in_stride && r_begin < r_end) ? fetch(r_begin, i) : 0.f; }
+  const int pe = threadIdx.x % SC, pp = threadIdx.x / SC, lane = threadIdx.x & 31;
+  for (int r = r_begin; r < r_end; r++) {
+    float* cur = in + ((r - r_begin) & 1) * in_stride;
+#pragma unroll
+    for (int u = 0; u < PF; u++) { const int i = threadIdx.x + u * nt; if (i < in_stride) cur[i] = pf[u]; }
+    for (int i = threadIdx.x + PF * nt; i < in_stride; i += nt) cur[i] = fetch(r, i);
+    if (r + 1 < r_end) {
+#pragma unroll
+      for (int u = 0; u < PF; u++) { const int i = threadIdx.x + u * nt; if (i < in_stride) pf[u] = fetch(r + 1, i); }
+    }
+    __syncthreads();
+    const float* sq = cur; const float* sk = cur + D; const float* sg = cur + 2 * D; const float* sv = cur + 3 * D;
+    // unit vectors: every warp sums the squares itself (the same values in the same order in every warp)
     float qq = 0.f, kk = 0.f;
-    for (int i = threadIdx.x; i < D; i += nt) {
-      const float a = x[hk * D + i], b = x[dl.kv_heads * D + hk * D + i];
-      qq = fmaf(a, a, qq);
-      kk = fmaf(b, b, kk);
-      sq[i] = a; sk[i] = b;
-      sg[i] = expf(-decay_rate * hyb_softplus(dt_raw[(size_t)r * dl.heads * D + h * D + i] + dl.dt_bias[h * D + i]));
-    }
-    qq = block_sum(qq, red);
-    kk = block_sum(kk, red);
+    for (int i = lane; i < D; i += 32) { qq = fmaf(sq[i], sq[i], qq); kk = fmaf(sk[i], sk[i], kk); }
+    qq = warp_sum(qq);
+    kk = warp_sum(kk);
     const float qn = qscale / sqrtf(qq + 1e-6f), kn = 1.0f / sqrtf(kk + 1e-6f);
-    const float beta = hyb_sigmoid(proj[(size_t)r * ldp + dl.o_b + h]);
-    // decay and S^T k
-    for (int idx = threadIdx.x; idx < parts * E; idx += nt) {
-      const int p = idx / E, e = idx - p * E;
+    if (pp < parts) {
       float acc = 0.f;
-      for (int d = p; d < D; d += parts) { const float v = S[d * E + e] * sg[d]; S[d * E + e] = v; acc = fmaf(v, sk[d] * kn, acc); }
-      part[idx] = acc;
+      for (int d = pp; d < D; d += parts) { const float v = S[d * SC + pe] * sg[d]; S[d * SC + pe] = v; acc = fmaf(v, sk[d] * kn, acc); }
+      part[pp * SC + pe] = acc;
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < E; e += nt) {
+    if (threadIdx.x < SC) {
       float acc = 0.f;
-      for (int p = 0; p < parts; p++) acc += part[p * E + e];
-      su[e] = beta * (x[2 * dl.kv_heads * D + h * E + e] - acc);
+      for (int p = 0; p < parts; p++) acc += part[p * SC + threadIdx.x];
+      su[threadIdx.x] = cur[3 * D + SC] * (sv[threadIdx.x] - acc);
     }
     __syncthreads();
-    // write and read-out
-    for (int idx = threadIdx.x; idx < parts * E; idx += nt) {
-      const int p = idx / E, e = idx - p * E;
-      const float u = su[e];
+    if (pp < parts) {
+      const float u = su[pe];
       float acc = 0.f;
-      for (int d = p; d < D; d += parts) { const float v = fmaf(sk[d] * kn, u, S[d * E + e]); S[d * E + e] = v; acc = fmaf(v, sq[d] * qn, acc); }
-      part[idx] = acc;
+      for (int d = pp; d < D; d += parts) { const float v = fmaf(sk[d] * kn, u, S[d * SC + pe]); S[d * SC + pe] = v; acc = fmaf(v, sq[d] * qn, acc); }
+      part[pp * SC + pe] = acc;
     }
     __syncthreads();
-    float ss = 0.f;
-    for (int e = threadIdx.x; e < E; e += nt) {
+    if (threadIdx.x < ec) {
       float acc = 0.f;
-      for (int p = 0; p < parts; p++) acc += part[p * E + e];
-      su[e] = acc;
-      ss = fmaf(acc, acc, ss);
+      for (int p = 0; p < parts; p++) acc += part[p * SC + threadIdx.x];
+      o_raw[(size_t)r * dl.heads * E + (size_t)h * E + e0 + threadIdx.x] = acc;
     }
-    ss = block_sum(ss, red);
-    const float inv = 1.0f / sqrtf(ss / (float)E + dl.eps);
-    for (int e = threadIdx.x; e < E; e += nt)
-      hyb_store(out + (size_t)r * dl.heads * E + (size_t)h * E + e,
-                su[e] * inv * dl.norm[e] * hyb_sigmoid(gate_raw[(size_t)r * dl.heads * E + h * E + e]));
-    __syncthreads();
   }
-  for (int i = threadIdx.x; i < D * E; i += nt) gstate[i] = S[i];
+  __syncthreads();
+  for (int i = threadIdx.x; i < D * SC; i += nt) { const int d = i / SC, e = i - d * SC; if (e < ec) gstate[(size_t)d * E + e0 + e] = S[i]; }
 }
 
 // ------------------------------------------------------------------------------------------------------------------
@@ -464,6 +876,13 @@ __global__ void hyb_glu_kernel(T* __restrict__ y, const float* __restrict__ gu, 
   hyb_store(y + i, g * hyb_sigmoid(alpha * g) * (u + 1.0f));
 }
 
+// THA_HYB_TC=0 keeps every product on the plain kernel (A/B aid)
+static bool hyb_tc_linear() {
+  static int on = -1;
+  if (on < 0) { const char* v = getenv("THA_HYB_TC"); on = (v && *v) ? atoi(v) != 0 : 1; }
+  return on != 0;
+}
+
 static int pick_threads(int want) {   // a multiple of 32 in 64..256
   int t = 64;
   while (t < want && t < 256) t += 32;
@@ -491,9 +910,23 @@ extern "C" int tha_hyb_linear(void* stream, int dtype, float* C, long long ldc, 
                               const int* group_off, int n_groups) {
   if (M < 1 || N < 1) return THA_STATUS_SUCCESS;
   if (K < 1 || !C || !A || !W) return THA_STATUS_INVALID_ARG;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == THA_DT_BF16 && !a_f32 && !a_rows && !group_off) {
+    // a plain bf16 product: the tcgen05 matmul of the bf16 model path (TMA-fed, fp32 accumulators in TMEM) when its
+    // alignment rules hold; the rows of this step are its activation columns
+    BfArgs b = {};
+    b.n_mats = 1; b.W[0] = (const uint16_t*)W; b.M[0] = N; b.out_off[0] = 0; b.K = K;
+    b.X = (const uint16_t*)A; b.N = M; b.ldx = lda;
+    b.out = C; b.ldo = ldc; b.zstride = 0; b.splits = 1; b.colscale = nullptr;
+    if (hyb_tc_linear() && gemm_bf16_ok(b)) return gemm_bf16_launch(s, b, false);
+  }
   const int mt = ceil_div(M, LT) + (group_off ? n_groups : 0);
   const dim3 grid(ceil_div(N, LT), mt), block(256);
-  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == THA_DT_BF16 && !a_f32 && hyb_tc_linear() && K % 8 == 0 && lda % 8 == 0 && w_group_stride % 8 == 0 && aligned16(A) && aligned16(W)) {
+    THA_CUDA_OK(launch(hyb_linear_mma_kernel, grid, dim3(128), 0, s, false, C, ldc, (const bf16*)A, lda, a_rows, (const bf16*)W, w_group_stride,
+                       M, N, K, group_off, n_groups));
+    return THA_STATUS_SUCCESS;
+  }
   if (dtype == THA_DT_F32)
     THA_CUDA_OK(launch(hyb_linear_kernel<float, float>, grid, block, 0, s, false, C, ldc, (const float*)A, lda, a_rows, (const float*)W,
                        w_group_stride, M, N, K, group_off, n_groups));
@@ -528,41 +961,61 @@ extern "C" int tha_hyb_attn_prepare(void* stream, const tha_attn_t* a, const tha
 extern "C" int tha_hyb_attn(void* stream, int dtype, const tha_attn_t* a, const tha_rows_t* rows, const tha_kv_t* kv, const float* q,
                             void* out) {
   if (rows->n_rows < 1) return THA_STATUS_SUCCESS;
-  const int nt = 128;
-  const int parts = nt / a->vdim > 0 ? nt / a->vdim : 1;
-  const int seen = rows->max_pos + 1;   // the most keys a query of this step can see
-  const int max_keys = a->chunk > 0 && a->chunk < seen ? a->chunk : seen;
-  const size_t smem = sizeof(float) * ((size_t)a->dim + max_keys + (size_t)parts * a->vdim);
+  if (a->heads % a->kv_heads || a->vdim > 32 * ATT_MAX_VC) return THA_STATUS_NOT_SUPPORTED;
+  const int gsize = a->heads / a->kv_heads;
+  const int AG = gsize < ATT_PAIRS ? gsize : ATT_PAIRS, AP = ATT_PAIRS / AG;
+  const size_t smem = sizeof(float) * ((size_t)ATT_PAIRS * a->dim + (size_t)ATT_KEYS * (a->dim + 1) + (size_t)ATT_KEYS * a->vdim + ATT_PAIRS * ATT_KEYS);
   if (smem > 227 * 1024) return THA_STATUS_NOT_SUPPORTED;
-  const dim3 grid(rows->n_rows, a->heads);
+  // position tiles: at most one ragged tile per sequence beyond rows / AP
+  const dim3 grid(rows->n_rows / AP + rows->n_seqs, a->kv_heads, ceil_div(gsize, AG));
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == THA_DT_BF16) {
     if (smem > 48 * 1024) THA_CUDA_OK(cudaFuncSetAttribute(hyb_attn_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    THA_CUDA_OK(launch(hyb_attn_kernel<bf16>, grid, dim3(nt), smem, s, false, *a, *rows, *kv, q, (bf16*)out));
+    THA_CUDA_OK(launch(hyb_attn_kernel<bf16>, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, (bf16*)out, AG, AP));
   } else {
     if (smem > 48 * 1024) THA_CUDA_OK(cudaFuncSetAttribute(hyb_attn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    THA_CUDA_OK(launch(hyb_attn_kernel<float>, grid, dim3(nt), smem, s, false, *a, *rows, *kv, q, (float*)out));
+    THA_CUDA_OK(launch(hyb_attn_kernel<float>, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, (float*)out, AG, AP));
   }
   return THA_STATUS_SUCCESS;
 }
 
-extern "C" int tha_hyb_mem_scan(void* stream, int dtype, const tha_mem_t* m, const tha_rows_t* rows, const tha_state_store_t* st,
-                                const float* proj, long long ldp, void* out) {
-  if (rows->n_seqs < 1) return THA_STATUS_SUCCESS;
-  const int nt = 256;
-  const int parts = nt / m->vdim > 0 ? nt / m->vdim : 1;
-  const size_t smem = sizeof(float) * ((size_t)m->dim * m->vdim + 3 * (size_t)m->dim + m->vdim + (size_t)parts * m->vdim);
-  const dim3 grid(rows->n_seqs, m->heads);
-  cudaStream_t s = (cudaStream_t)stream;
-  if (smem > 227 * 1024) return THA_STATUS_NOT_SUPPORTED;
-  if (dtype == THA_DT_BF16) {
-    if (smem > 48 * 1024) THA_CUDA_OK(cudaFuncSetAttribute(hyb_mem_scan_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    THA_CUDA_OK(launch(hyb_mem_scan_kernel<bf16>, grid, dim3(nt), smem, s, false, *m, *rows, *st, proj, ldp, (bf16*)out));
-  } else {
-    if (smem > 48 * 1024) THA_CUDA_OK(cudaFuncSetAttribute(hyb_mem_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    THA_CUDA_OK(launch(hyb_mem_scan_kernel<float>, grid, dim3(nt), smem, s, false, *m, *rows, *st, proj, ldp, (float*)out));
-  }
+// THA_HYB_SCAN=shared keeps the shared-memory scans at every head size (A/B aid and the test of that form)
+static bool scan_in_registers() {
+  const char* v = getenv("THA_HYB_SCAN");
+  return !(v && !strcmp(v, "shared"));
+}
+// columns per block of the scans: a power of two that divides the thread count
+static int scan_slice(int vdim) { int sc = 1; while (sc < vdim && sc < 16) sc <<= 1; return sc; }
+
+template <typename T>
+static int head_gate_launch(cudaStream_t s, T* out, const float* o_raw, int n_rows, int heads, int E, float eps, const float* norm,
+                            int norm_per_head, const float* gate, long long ldg) {
+  THA_CUDA_OK(launch(hyb_head_gate_kernel<T>, dim3(ceil_div(n_rows * heads, 4)), dim3(128), 0, s, false, out, o_raw, n_rows, heads, E, eps, norm,
+                     norm_per_head, gate, ldg));
   return THA_STATUS_SUCCESS;
+}
+
+extern "C" int tha_hyb_mem_scan(void* stream, int dtype, const tha_mem_t* m, const tha_rows_t* rows, const tha_state_store_t* st,
+                                const float* proj, long long ldp, float* o_raw, void* out) {
+  if (rows->n_seqs < 1) return THA_STATUS_SUCCESS;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (m->dim <= 256 && scan_in_registers()) {
+    const dim3 grid(rows->n_seqs, m->heads, ceil_div(m->vdim, SCW * SCAN_WARPS)), block(32 * SCAN_WARPS);
+    if (m->dim <= 32) THA_CUDA_OK(launch(hyb_mem_scan_warp_kernel<1>, grid, block, 0, s, false, *m, *rows, *st, proj, ldp, o_raw));
+    else if (m->dim <= 64) THA_CUDA_OK(launch(hyb_mem_scan_warp_kernel<2>, grid, block, 0, s, false, *m, *rows, *st, proj, ldp, o_raw));
+    else if (m->dim <= 128) THA_CUDA_OK(launch(hyb_mem_scan_warp_kernel<4>, grid, block, 0, s, false, *m, *rows, *st, proj, ldp, o_raw));
+    else THA_CUDA_OK(launch(hyb_mem_scan_warp_kernel<8>, grid, block, 0, s, false, *m, *rows, *st, proj, ldp, o_raw));
+  } else {
+    const int SC = scan_slice(m->vdim), parts = SCAN_THREADS / SC;
+    const size_t smem = sizeof(float) * ((size_t)m->dim * SC + m->dim + 2 * (2 * (size_t)m->dim + SC + 2) + (size_t)parts * SC);
+    if (smem > 227 * 1024) return THA_STATUS_NOT_SUPPORTED;
+    const dim3 grid(rows->n_seqs, m->heads, ceil_div(m->vdim, SC));
+    if (smem > 48 * 1024) THA_CUDA_OK(cudaFuncSetAttribute(hyb_mem_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    THA_CUDA_OK(launch(hyb_mem_scan_kernel, grid, dim3(SCAN_THREADS), smem, s, false, *m, *rows, *st, proj, ldp, o_raw, SC));
+  }
+  const float* gate = proj + m->o_g;
+  if (dtype == THA_DT_BF16) return head_gate_launch(s, (bf16*)out, o_raw, rows->n_rows, m->heads, m->vdim, m->eps, m->norm, 1, gate, ldp);
+  return head_gate_launch(s, (float*)out, o_raw, rows->n_rows, m->heads, m->vdim, m->eps, m->norm, 1, gate, ldp);
 }
 
 extern "C" int tha_hyb_conv_silu(void* stream, const tha_rows_t* rows, const tha_state_store_t* st, long long conv_state_off,
@@ -580,23 +1033,27 @@ extern "C" int tha_hyb_conv_silu(void* stream, const tha_rows_t* rows, const tha
 
 extern "C" int tha_hyb_delta_scan(void* stream, int dtype, const tha_delta_t* d, const tha_rows_t* rows, const tha_state_store_t* st,
                                   const float* qkv, const float* proj, long long ldp, const float* dt_raw, const float* gate_raw,
-                                  void* out) {
+                                  float* o_raw, void* out) {
   if (rows->n_seqs < 1) return THA_STATUS_SUCCESS;
   if (d->heads % d->kv_heads) return THA_STATUS_INVALID_ARG;
-  const int nt = 256;
-  const int parts = nt / d->vdim > 0 ? nt / d->vdim : 1;
-  const size_t smem = sizeof(float) * ((size_t)d->dim * d->vdim + 3 * (size_t)d->dim + d->vdim + (size_t)parts * d->vdim);
-  if (smem > 227 * 1024) return THA_STATUS_NOT_SUPPORTED;
-  const dim3 grid(rows->n_seqs, d->heads);
   cudaStream_t s = (cudaStream_t)stream;
-  if (dtype == THA_DT_BF16) {
-    if (smem > 48 * 1024) THA_CUDA_OK(cudaFuncSetAttribute(hyb_delta_scan_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    THA_CUDA_OK(launch(hyb_delta_scan_kernel<bf16>, grid, dim3(nt), smem, s, false, *d, *rows, *st, qkv, proj, ldp, dt_raw, gate_raw, (bf16*)out));
+  if (d->dim <= 256 && scan_in_registers()) {
+    const dim3 grid(rows->n_seqs, d->heads, ceil_div(d->vdim, SCW * SCAN_WARPS)), block(32 * SCAN_WARPS);
+    if (d->dim <= 32) THA_CUDA_OK(launch(hyb_delta_scan_warp_kernel<1>, grid, block, 0, s, false, *d, *rows, *st, qkv, proj, ldp, dt_raw, o_raw));
+    else if (d->dim <= 64) THA_CUDA_OK(launch(hyb_delta_scan_warp_kernel<2>, grid, block, 0, s, false, *d, *rows, *st, qkv, proj, ldp, dt_raw, o_raw));
+    else if (d->dim <= 128) THA_CUDA_OK(launch(hyb_delta_scan_warp_kernel<4>, grid, block, 0, s, false, *d, *rows, *st, qkv, proj, ldp, dt_raw, o_raw));
+    else THA_CUDA_OK(launch(hyb_delta_scan_warp_kernel<8>, grid, block, 0, s, false, *d, *rows, *st, qkv, proj, ldp, dt_raw, o_raw));
   } else {
-    if (smem > 48 * 1024) THA_CUDA_OK(cudaFuncSetAttribute(hyb_delta_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    THA_CUDA_OK(launch(hyb_delta_scan_kernel<float>, grid, dim3(nt), smem, s, false, *d, *rows, *st, qkv, proj, ldp, dt_raw, gate_raw, (float*)out));
+    const int SC = scan_slice(d->vdim), parts = SCAN_THREADS / SC;
+    const size_t smem = sizeof(float) * ((size_t)d->dim * SC + 2 * (3 * (size_t)d->dim + SC + 1) + (size_t)parts * SC + SC);
+    if (smem > 227 * 1024) return THA_STATUS_NOT_SUPPORTED;
+    const dim3 grid(rows->n_seqs, d->heads, ceil_div(d->vdim, SC));
+    if (smem > 48 * 1024) THA_CUDA_OK(cudaFuncSetAttribute(hyb_delta_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    THA_CUDA_OK(launch(hyb_delta_scan_kernel, grid, dim3(SCAN_THREADS), smem, s, false, *d, *rows, *st, qkv, proj, ldp, dt_raw, o_raw, SC));
   }
-  return THA_STATUS_SUCCESS;
+  const long long ldg = (long long)d->heads * d->vdim;
+  if (dtype == THA_DT_BF16) return head_gate_launch(s, (bf16*)out, o_raw, rows->n_rows, d->heads, d->vdim, d->eps, d->norm, 0, gate_raw, ldg);
+  return head_gate_launch(s, (float*)out, o_raw, rows->n_rows, d->heads, d->vdim, d->eps, d->norm, 0, gate_raw, ldg);
 }
 
 extern "C" int tha_hyb_moe_route(void* stream, const tha_moe_t* e, const float* proj, long long ldp, int n_rows, int* expert_id,

@@ -70,7 +70,7 @@ struct Carver {
 };
 
 struct StepBuffers {
-  float *x, *proj, *q, *left, *right, *conv, *dt_raw, *gate_raw, *gu, *down, *sdown, *weight;
+  float *x, *proj, *q, *left, *right, *conv, *dt_raw, *gate_raw, *gu, *down, *sdown, *weight, *oraw;
   void *h, *abuf, *mbuf, *y, *sy, *hn;
   int *expert_id, *group_off, *sorted_row, *inv;
   float* cos_t[16]; float* sin_t[16];
@@ -107,6 +107,7 @@ static size_t carve(const tha_hyb_model_t* m, int R, int n_want, char* base, Ste
   b->q = c.take<float>(R * qd);
   b->abuf = c.take<char>(R * av * es);
   b->mbuf = c.take<char>(R * mv * es);
+  b->oraw = c.take<float>(R * mv);
   b->left = c.take<float>(R * W);
   b->right = c.take<float>(R * W);
   b->conv = c.take<float>(R * cc);
@@ -184,7 +185,7 @@ extern "C" int tha_hyb_step(void* stream, const tha_hyb_model_t* m, const tha_ro
       HYB_OK(tha_hyb_attn(stream, dt, &a, rows, kv, b.q, b.abuf));
       HYB_OK(tha_hyb_linear(stream, dt, b.left, W, b.abuf, a.heads * a.vdim, 0, nullptr, a.w_o, 0, R, W, a.heads * a.vdim, nullptr, 0));
       const tha_mem_t& mm = L.mem;
-      HYB_OK(tha_hyb_mem_scan(stream, dt, &mm, rows, st, b.proj, ldp, b.mbuf));
+      HYB_OK(tha_hyb_mem_scan(stream, dt, &mm, rows, st, b.proj, ldp, b.oraw, b.mbuf));
       HYB_OK(tha_hyb_linear(stream, dt, b.right, W, b.mbuf, mm.heads * mm.vdim, 0, nullptr, mm.w_o, 0, R, W, mm.heads * mm.vdim, nullptr, 0));
       right = b.right;
     } else if (L.mixer == THA_MIX_DELTA) {
@@ -193,7 +194,7 @@ extern "C" int tha_hyb_step(void* stream, const tha_hyb_model_t* m, const tha_ro
       HYB_OK(tha_hyb_conv_silu(stream, rows, st, d.conv_state_off, b.proj, ldp, d.o_q, C, d.taps, d.conv, b.conv));
       HYB_OK(tha_hyb_linear(stream, dt, b.dt_raw, d.heads * d.dim, b.proj + d.o_a1, ldp, 1, nullptr, d.w_a2, 0, R, d.heads * d.dim, d.rank_a, nullptr, 0));
       HYB_OK(tha_hyb_linear(stream, dt, b.gate_raw, d.heads * d.vdim, b.proj + d.o_g1, ldp, 1, nullptr, d.w_g2, 0, R, d.heads * d.vdim, d.rank_g, nullptr, 0));
-      HYB_OK(tha_hyb_delta_scan(stream, dt, &d, rows, st, b.conv, b.proj, ldp, b.dt_raw, b.gate_raw, b.mbuf));
+      HYB_OK(tha_hyb_delta_scan(stream, dt, &d, rows, st, b.conv, b.proj, ldp, b.dt_raw, b.gate_raw, b.oraw, b.mbuf));
       HYB_OK(tha_hyb_linear(stream, dt, b.left, W, b.mbuf, d.heads * d.vdim, 0, nullptr, d.w_o, 0, R, W, d.heads * d.vdim, nullptr, 0));
     } else {
       return THA_STATUS_NOT_SUPPORTED;

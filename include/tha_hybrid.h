@@ -180,9 +180,10 @@ int tha_hyb_attn_prepare(void* stream, const tha_attn_t* a, const tha_rows_t* ro
 int tha_hyb_attn(void* stream, int dtype, const tha_attn_t* a, const tha_rows_t* rows, const tha_kv_t* kv, const float* q,
                  void* out);
 /* the matrix memory over the rows of every sequence in order, state read from and written back to the slots;
+ * o_raw: fp32 scratch [n_rows, heads * vdim] (the read-out before the head norm);
  * out dtype-typed [n_rows, heads * vdim] = unit-rms per head * norm * sigmoid(gate) */
 int tha_hyb_mem_scan(void* stream, int dtype, const tha_mem_t* m, const tha_rows_t* rows, const tha_state_store_t* st,
-                     const float* proj, long long ldp, void* out);
+                     const float* proj, long long ldp, float* o_raw, void* out);
 /* causal convolution + silu over `channels` adjacent columns of proj starting at col0, continuing from the slot's
  * tail; out fp32 [n_rows, channels]; then the tails are advanced */
 int tha_hyb_conv_silu(void* stream, const tha_rows_t* rows, const tha_state_store_t* st, long long conv_state_off,
@@ -191,7 +192,7 @@ int tha_hyb_conv_silu(void* stream, const tha_rows_t* rows, const tha_state_stor
  * and gate_raw [n_rows, heads*vdim] the outputs of the two low-rank projections (before bias / softplus / sigmoid) */
 int tha_hyb_delta_scan(void* stream, int dtype, const tha_delta_t* d, const tha_rows_t* rows, const tha_state_store_t* st,
                        const float* qkv, const float* proj, long long ldp, const float* dt_raw, const float* gate_raw,
-                       void* out);
+                       float* o_raw, void* out);
 /* router: expert ids and weights [n_rows, top]; rows sorted by expert: group_off (2 * (experts + 1) ints: the offsets,
  * then scratch), sorted_row [n_rows * top] and the position of (row, j) in that order, inv [n_rows * top] */
 int tha_hyb_moe_route(void* stream, const tha_moe_t* e, const float* proj, long long ldp, int n_rows, int* expert_id,

@@ -378,3 +378,21 @@ def test_sampled_generation_is_reproducible_and_independent_of_the_batch(general
     assert a == b
     c = general.engine(max_seqs=2).generate(prompts, [10, 10], temperature=1.0, topp=0.9, seed=8)
     assert a != c
+
+
+def test_shared_memory_form_of_the_scans(general, monkeypatch):
+    """Heads of more than 256 key channels take the scans that keep the state in shared memory; the switch forces that
+    form at the test's sizes."""
+    monkeypatch.setenv("THA_HYB_SCAN", "shared")
+    toks = tokens_for(general, 90, 13)
+    z, _ = general.ref(toks)
+    assert rel_err(feed(general.engine(), "a", toks, [33, 2, 1]), z) < F32_TOL
+
+
+def test_plain_products_everywhere(general, monkeypatch):
+    """bfloat16 without the tensor-core products (the form odd sizes fall back to)."""
+    monkeypatch.setenv("THA_HYB_TC", "0")
+    # the switch is read once per process: only meaningful when this test runs first; otherwise it repeats the default
+    toks = tokens_for(general, 60, 14)
+    z, _ = general.ref(toks)
+    assert rel_err(feed(general.engine("bfloat16"), "a", toks, [60]), z) < BF16_TOL
