@@ -10,12 +10,25 @@
 // -q 1 host-side sampler, -c <blocks> paged KV cache,
 // and in test mode -t/-p/-s are honoured when given (-t 0 = greedy).  The checkpoint may be a
 // v0 fp32 file or a v2 Q8_0 file; the version is detected from the header.
+//
+// A FOLDER with config.json + model.safetensors is a layer-program model (include/layer_model.hpp): its "architecture"
+// key picks the registered design, requests run through the SequenceEngine (continuous batching, prompts in portions
+// beside decoding requests) and the same device sampler.  Such models carry no tokenizer: -i and the lines of -f are
+// token ids separated by blanks or commas, the output is token ids.  -b = live requests, -d bf16|f32 the number format,
+// -j the most prompt tokens per step, -c the cache pool in positions (default: what the requests need).
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
 #include <time.h>
 
+#include <fstream>
+#include <sstream>
+#include <string>
+#include <vector>
+
+#include "layer_model.hpp"
 #include "llama_driver.hpp"
+#include "sequence_engine.hpp"
 
 static void error_usage() {
   fprintf(stderr, "Usage:   llama <checkpoint> [options]\n");
@@ -38,8 +51,78 @@ static void error_usage() {
   fprintf(stderr, "  -x <0|1>    ignore stop tokens (fixed-length timing runs)\n");
   fprintf(stderr, "  -c <int>    paged KV cache: the slots of a GPU share this many blocks of 16 positions (-1: what fits; default 0: dense slabs)\n");
   fprintf(stderr, "  -q <0|1>    sampled runs: 1 = sample on the host from B*vocab logits as the reference does (default 0: sampler on the GPU)\n");
+  fprintf(stderr, "  -d <bf16|f32> model folders (config.json + model.safetensors): number format, default bf16; -i / -f carry token ids\n");
+  fprintf(stderr, "  -j <int>    model folders: the most prompt tokens per scheduler step (default 256)\n");
   fprintf(stderr, "  -r <0|1>    fp32 models: ingest prompts in one tensor-core pass (default 1); 0 = one decode step per prompt token\n");
   exit(EXIT_FAILURE);
+}
+
+static std::vector<int> parse_ids(const std::string& text) {
+  std::vector<int> out;
+  std::string cur;
+  for (char c : text + " ") {
+    if ((c >= '0' && c <= '9')) cur += c;
+    else if (!cur.empty()) { out.push_back(atoi(cur.c_str())); cur.clear(); }
+  }
+  return out;
+}
+
+// generate / test modes for a layer-program model folder
+static int run_layer_program(const char* folder, const char* mode, const char* prompt, const char* input_filename, const char* output_filename,
+                             int steps, int batch, float temperature, float topp, unsigned long long seed, const char* number_format,
+                             int portion, int pool_positions) {
+  const int dtype = (!strcmp(number_format, "f32") || !strcmp(number_format, "float32")) ? THA_DT_F32 : THA_DT_BF16;
+  std::vector<GenerationRequest> reqs;
+  if (!strcmp(mode, "generate")) {
+    GenerationRequest q;
+    q.prompt = parse_ids(prompt ? prompt : "");
+    reqs.push_back(q);
+  } else if (!strcmp(mode, "test")) {
+    if (!input_filename || !output_filename) error_usage();
+    std::ifstream in(input_filename);
+    if (!in) { fprintf(stderr, "cannot open %s\n", input_filename); return EXIT_FAILURE; }
+    std::string line;
+    while (std::getline(in, line)) {
+      GenerationRequest q;
+      q.prompt = parse_ids(line);
+      if (!q.prompt.empty()) reqs.push_back(q);
+    }
+  } else {
+    fprintf(stderr, "unknown mode: %s\n", mode);
+    error_usage();
+  }
+  size_t need = 0, longest = 0;
+  for (auto& q : reqs) {
+    if (q.prompt.empty()) { fprintf(stderr, "a request needs token ids (-i \"1 2 3\")\n"); return EXIT_FAILURE; }
+    q.max_new = steps > 0 ? steps : 256;
+    const size_t n = (q.prompt.size() + q.max_new + 63) / 64 * 64;
+    longest = n > longest ? n : longest;
+  }
+  need = longest * (size_t)(batch < (int)reqs.size() ? batch : (int)reqs.size());
+  std::string err;
+  const long load_start = time_in_ms();
+  LayerModel* model = LayerModel::load(folder, dtype, &err);
+  if (!model) { fprintf(stderr, "%s\n", err.c_str()); return EXIT_FAILURE; }
+  SequenceEngine engine(model, pool_positions > 0 ? pool_positions : (int)need, batch);
+  if (!engine.ok()) { fprintf(stderr, "%s\n", engine.error().c_str()); return EXIT_FAILURE; }
+  SamplingOptions so;
+  so.temperature = temperature; so.topp = topp; so.seed = seed;
+  const long start = time_in_ms();
+  if (!engine.generate(&reqs, so, portion)) { fprintf(stderr, "%s\n", engine.error().c_str()); return EXIT_FAILURE; }
+  const long end = time_in_ms();
+  size_t total = 0;
+  FILE* out = output_filename ? fopen(output_filename, "w") : stdout;
+  if (!out) { fprintf(stderr, "cannot write %s\n", output_filename); return EXIT_FAILURE; }
+  for (auto& q : reqs) {
+    for (size_t i = 0; i < q.output.size(); i++) fprintf(out, i ? " %d" : "%d", q.output[i]);
+    fprintf(out, "\n");
+    total += q.output.size();
+  }
+  if (output_filename) fclose(out);
+  fprintf(stderr, "weight upload(s): %f, %lld steps, achieved tok/s: %f\n", (start - load_start) / 1000.0, engine.steps_run(),
+          total / (double)(end - start + 1) * 1000);
+  delete model;
+  return 0;
 }
 
 int main(int argc, char* argv[]) {
@@ -51,7 +134,8 @@ int main(int argc, char* argv[]) {
   const char* prompt = nullptr;
   unsigned long long rng_seed = 0;
   const char* mode = "generate";
-  const char *input_filename = nullptr, *output_filename = nullptr, *token_filename = nullptr;
+  const char *input_filename = nullptr, *output_filename = nullptr, *token_filename = nullptr, *number_format = "bf16";
+  int portion = 256;
   bool t_given = false, s_given = false, n_given = false;
 
   if (argc >= 2) checkpoint_path = argv[1]; else error_usage();
@@ -77,6 +161,8 @@ int main(int argc, char* argv[]) {
     else if (f == 'w') tp = atoi(v);
     else if (f == 'q') host_sampler = atoi(v);
     else if (f == 'c') kv_blocks = atoi(v);
+    else if (f == 'd') number_format = v;
+    else if (f == 'j') portion = atoi(v);
     else error_usage();
   }
   if (rng_seed == 0) rng_seed = (unsigned int)time(nullptr);
@@ -85,6 +171,14 @@ int main(int argc, char* argv[]) {
   if (steps < 0) steps = 0;
   if (batch < 1) batch = 1;
 
+  {   // the registry decides which family the path belongs to
+    std::string err;
+    const ArchitectureEntry* arch = detect_model(checkpoint_path, nullptr, &err);
+    if (!arch) { fprintf(stderr, "%s\n", err.c_str()); return EXIT_FAILURE; }
+    if (arch->family == ModelFamily::LayerProgram)
+      return run_layer_program(checkpoint_path, mode, prompt, input_filename, output_filename, n_given ? steps : 0, batch,
+                               t_given ? temperature : 0.0f, topp, rng_seed, number_format, portion, kv_blocks);
+  }
   const int version = checkpoint_version(checkpoint_path);
   if (version != 0 && version != 2) { fprintf(stderr, "unreadable checkpoint %s\n", checkpoint_path); return EXIT_FAILURE; }
   Transformer t32;

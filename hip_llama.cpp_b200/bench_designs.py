@@ -72,11 +72,26 @@ def _time_timerax(serving, folder, prompt_len, batch, ctx, steps, warmup, kernel
     for k in range(warmup + steps):
         entries = [(i, [int(rng.integers(0, vocab))], [0]) for i in ids]
         t0 = time.perf_counter()
-        eng.step(entries)
+        eng.step(entries, copy=False)
         times.append(time.perf_counter() - t0)
     ms = 1e3 * float(np.median(times[warmup:]))
-    out["decode"] = {"batch": batch, "context": ctx, "ms_per_step": ms, "tok_s": batch / ms * 1e3}
+    out["decode"] = {"batch": batch, "context": ctx, "ms_per_step": ms, "tok_s": batch / ms * 1e3,
+                     "what": "one token per request per step, every request's logits back in pinned host memory"}
+    for i in ids:
+        eng.finish(i)
+    # generation through the scheduler (device sampler, token ids back): two calls that differ in length only
+    prompts = [rng.integers(0, vocab, ctx).tolist() for _ in range(batch)]
+    t = []
+    for new in (2, 2 + steps):
+        t0 = time.perf_counter()
+        eng.generate(prompts, [new] * batch, temperature=0.0, portion=4096)
+        t.append(time.perf_counter() - t0)
+    ms = 1e3 * (t[1] - t[0]) / steps
+    out["generate"] = {"batch": batch, "context": ctx, "ms_per_step": ms, "tok_s": batch / ms * 1e3,
+                       "what": "greedy generation through SequenceEngine.generate, time of %d extra tokens per request" % steps}
     if kernels:
+        for i in ids:
+            eng.step([(i, rng.integers(0, vocab, ctx).tolist(), [])])
         cuda.tha_trace_dump(1 << 30)
         eng.step([(i, [1], [0]) for i in ids])
         print(f"# kernels of one decode step, {batch} requests at context {ctx}", flush=True)
@@ -89,7 +104,7 @@ def _time_llama(engine_mod, checkpoint_mod, s, prompt_len, batch, ctx, steps, wa
     import torch
     hidden = s["top"] * s["ff"] + s["sff"]
     cfg = checkpoint_mod.Config(dim=s["width"], hidden_dim=hidden, n_layers=s["layers"], n_heads=s["heads"], n_kv_heads=s["kv_heads"],
-                                vocab_size=s["vocab"], seq_len=max(prompt_len, ctx + steps + warmup + 8))
+                                vocab_size=s["vocab"], seq_len=max(prompt_len, ctx + 2 * (steps + warmup) + 8))
     dw = engine_mod.DeviceWeightsBF16.random(cfg, seed=1, device="cuda")
     out = {"weights_bytes": dw.nbytes()}
     e = engine_mod.Engine(dw, max(batch, 1), device="cuda", with_att=False)
@@ -119,6 +134,15 @@ def _time_llama(engine_mod, checkpoint_mod, s, prompt_len, batch, ctx, steps, wa
             times.append(time.perf_counter() - t0)
         ms = 1e3 * float(np.median(times[warmup:]))
         out["decode"] = {"batch": batch, "context": ctx, "ms_per_step": ms, "tok_s": batch / ms * 1e3}
+        times = []
+        for k in range(warmup + steps):
+            tok = rng.integers(3, cfg.vocab_size, size=batch).astype(np.int32)
+            pos = np.full(batch, ctx + warmup + steps + k, np.int32)
+            t0 = time.perf_counter()
+            e.forward_greedy(tok, pos, stream=st)          # host tokens in, greedy token ids back
+            times.append(time.perf_counter() - t0)
+        ms = 1e3 * float(np.median(times[warmup:]))
+        out["generate"] = {"batch": batch, "context": ctx, "ms_per_step": ms, "tok_s": batch / ms * 1e3}
     return out
 
 

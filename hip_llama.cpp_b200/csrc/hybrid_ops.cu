@@ -291,11 +291,13 @@ constexpr int ATT_PAIRS = 16, ATT_KEYS = 32, ATT_MAX_VC = 8;   // value channels
 template <typename T>
 __global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t rows, tha_kv_t kv, const float* __restrict__ q,
                                                        T* __restrict__ out, int AG, int AP) {
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   const int D = a.dim, E = a.vdim, gsize = a.heads / a.kv_heads;
+  const bool vec = ((D | E) & 3) == 0;         // 128-bit shared-memory reads: rows padded to keep them aligned and conflict-free
+  const int KS = vec ? D + 4 : D + 1;
   float* Qs = sm;                              // [16][D]
-  float* Ks = Qs + ATT_PAIRS * D;              // [32][D + 1]
-  float* Vs = Ks + ATT_KEYS * (D + 1);         // [32][E]
+  float* Ks = Qs + ATT_PAIRS * D;              // [32][KS]
+  float* Vs = Ks + ATT_KEYS * KS;              // [32][E]
   float* Ps = Vs + ATT_KEYS * E;               // [16][32]
   // which sequence and which positions: tiles of AP rows per sequence, found by walking the sequences
   int seq = -1, r0 = 0, r_end = 0;
@@ -336,7 +338,8 @@ __global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t 
   const int key_lo = a.chunk > 0 ? (p_first / a.chunk) * a.chunk : 0;
   for (int kt = (key_lo / ATT_KEYS) * ATT_KEYS; kt <= p_last; kt += ATT_KEYS) {
     __syncthreads();   // the previous tile is consumed (and Qs is written, the first time)
-    // a warp fetches 8 keys: all 8 table entries first, then the rows, so that the loads are in flight together
+    // a warp fetches 8 keys: all 8 table entries first, then the rows four at a time into registers before any of them
+    // goes to shared memory, so that the loads are in flight together (a load followed by its own store waits for it)
     size_t krow[ATT_KEYS / 4];
 #pragma unroll
     for (int jj = 0; jj < ATT_KEYS / 4; jj++) {
@@ -344,24 +347,57 @@ __global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t 
       krow[jj] = (t <= p_last && t >= key_lo) ? hyb_kv_row(kv, slot, t, a.cache_layer) : (size_t)-1;
     }
 #pragma unroll
-    for (int jj = 0; jj < ATT_KEYS / 4; jj++) {
-      const int j = warp + 4 * jj;
-      const bool live = krow[jj] != (size_t)-1;
-      const float* kr = kv.k_pool + (live ? krow[jj] : 0) + (size_t)g * D;
-      const float* vr = kv.v_pool + (live ? krow[jj] : 0) + (size_t)g * E;
-      for (int d = lane; d < D; d += 32) Ks[j * (D + 1) + d] = live ? kr[d] : 0.f;
-      for (int e = lane; e < E; e += 32) Vs[j * E + e] = live ? vr[e] : 0.f;
+    for (int which = 0; which < 2; which++) {
+      const float* pool = which ? kv.v_pool : kv.k_pool;
+      const int width = which ? E : D, stride = which ? E : KS;
+      float* dst = which ? Vs : Ks;
+#pragma unroll
+      for (int j0 = 0; j0 < ATT_KEYS / 4; j0 += 4) {
+        float buf[4][ATT_MAX_VC];
+#pragma unroll
+        for (int jj = 0; jj < 4; jj++) {
+          const bool live = krow[j0 + jj] != (size_t)-1;
+          const float* src = pool + (live ? krow[j0 + jj] : 0) + (size_t)g * width;
+#pragma unroll
+          for (int c = 0; c < ATT_MAX_VC; c++) buf[jj][c] = (live && lane + 32 * c < width) ? __ldg(src + lane + 32 * c) : 0.f;
+        }
+#pragma unroll
+        for (int jj = 0; jj < 4; jj++) {
+          const int j = warp + 4 * (j0 + jj);
+#pragma unroll
+          for (int c = 0; c < ATT_MAX_VC; c++)
+            if (lane + 32 * c < width) dst[j * stride + lane + 32 * c] = buf[jj][c];
+          if (width > 32 * ATT_MAX_VC) {   // wider key rows than the register buffer: the rest one by one
+            const bool live = krow[j0 + jj] != (size_t)-1;
+            const float* src = pool + (live ? krow[j0 + jj] : 0) + (size_t)g * width;
+            for (int d = lane + 32 * ATT_MAX_VC; d < width; d += 32) dst[j * stride + d] = live ? src[d] : 0.f;
+          }
+        }
+      }
     }
     __syncthreads();
     float sc[4] = {0.f, 0.f, 0.f, 0.f};
-    const float* kl = Ks + lane * (D + 1);
+    const float* kl = Ks + lane * KS;
     const float* q0 = Qs + (warp * 4) * D;
-    for (int d = 0; d < D; d++) {
-      const float kd = kl[d];
-      sc[0] = fmaf(q0[d], kd, sc[0]);
-      sc[1] = fmaf(q0[D + d], kd, sc[1]);
-      sc[2] = fmaf(q0[2 * D + d], kd, sc[2]);
-      sc[3] = fmaf(q0[3 * D + d], kd, sc[3]);
+    if (vec) {
+      const float4* k4 = reinterpret_cast<const float4*>(kl);
+      const float4* qa = reinterpret_cast<const float4*>(q0);
+      const int D4 = D >> 2;
+      for (int d = 0; d < D4; d++) {
+        const float4 kd = k4[d];
+        sc[0] = dot4(qa[d], kd, sc[0]);
+        sc[1] = dot4(qa[D4 + d], kd, sc[1]);
+        sc[2] = dot4(qa[2 * D4 + d], kd, sc[2]);
+        sc[3] = dot4(qa[3 * D4 + d], kd, sc[3]);
+      }
+    } else {
+      for (int d = 0; d < D; d++) {
+        const float kd = kl[d];
+        sc[0] = fmaf(q0[d], kd, sc[0]);
+        sc[1] = fmaf(q0[D + d], kd, sc[1]);
+        sc[2] = fmaf(q0[2 * D + d], kd, sc[2]);
+        sc[3] = fmaf(q0[3 * D + d], kd, sc[3]);
+      }
     }
     const int t = kt + lane;
 #pragma unroll
@@ -382,17 +418,41 @@ __global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t 
     }
     __syncwarp();
     const float* pw = Ps + (warp * 4) * ATT_KEYS;
-    for (int j = 0; j < ATT_KEYS; j++) {
-      const float p0 = pw[j], p1 = pw[ATT_KEYS + j], p2 = pw[2 * ATT_KEYS + j], p3 = pw[3 * ATT_KEYS + j];
+    if (vec) {
+      const float4* p4 = reinterpret_cast<const float4*>(pw);
+      for (int j4 = 0; j4 < ATT_KEYS / 4; j4++) {
+        const float4 pa = p4[j4], pb = p4[ATT_KEYS / 4 + j4], pc = p4[2 * (ATT_KEYS / 4) + j4], pd = p4[3 * (ATT_KEYS / 4) + j4];
+        const float P0[4] = {pa.x, pa.y, pa.z, pa.w}, P1[4] = {pb.x, pb.y, pb.z, pb.w}, P2[4] = {pc.x, pc.y, pc.z, pc.w},
+                    P3[4] = {pd.x, pd.y, pd.z, pd.w};
 #pragma unroll
-      for (int c = 0; c < ATT_MAX_VC; c++) {
-        const int e = lane + 32 * c;
-        if (e < E) {
-          const float v = Vs[j * E + e];
-          acc[0][c] = fmaf(p0, v, acc[0][c]);
-          acc[1][c] = fmaf(p1, v, acc[1][c]);
-          acc[2][c] = fmaf(p2, v, acc[2][c]);
-          acc[3][c] = fmaf(p3, v, acc[3][c]);
+        for (int jj = 0; jj < 4; jj++) {
+          const float* vrow = Vs + (4 * j4 + jj) * E;
+#pragma unroll
+          for (int c = 0; c < ATT_MAX_VC; c++) {
+            const int e = lane + 32 * c;
+            if (e < E) {
+              const float v = vrow[e];
+              acc[0][c] = fmaf(P0[jj], v, acc[0][c]);
+              acc[1][c] = fmaf(P1[jj], v, acc[1][c]);
+              acc[2][c] = fmaf(P2[jj], v, acc[2][c]);
+              acc[3][c] = fmaf(P3[jj], v, acc[3][c]);
+            }
+          }
+        }
+      }
+    } else {
+      for (int j = 0; j < ATT_KEYS; j++) {
+        const float p0 = pw[j], p1 = pw[ATT_KEYS + j], p2 = pw[2 * ATT_KEYS + j], p3 = pw[3 * ATT_KEYS + j];
+#pragma unroll
+        for (int c = 0; c < ATT_MAX_VC; c++) {
+          const int e = lane + 32 * c;
+          if (e < E) {
+            const float v = Vs[j * E + e];
+            acc[0][c] = fmaf(p0, v, acc[0][c]);
+            acc[1][c] = fmaf(p1, v, acc[1][c]);
+            acc[2][c] = fmaf(p2, v, acc[2][c]);
+            acc[3][c] = fmaf(p3, v, acc[3][c]);
+          }
         }
       }
     }
@@ -964,7 +1024,7 @@ extern "C" int tha_hyb_attn(void* stream, int dtype, const tha_attn_t* a, const 
   if (a->heads % a->kv_heads || a->vdim > 32 * ATT_MAX_VC) return THA_STATUS_NOT_SUPPORTED;
   const int gsize = a->heads / a->kv_heads;
   const int AG = gsize < ATT_PAIRS ? gsize : ATT_PAIRS, AP = ATT_PAIRS / AG;
-  const size_t smem = sizeof(float) * ((size_t)ATT_PAIRS * a->dim + (size_t)ATT_KEYS * (a->dim + 1) + (size_t)ATT_KEYS * a->vdim + ATT_PAIRS * ATT_KEYS);
+  const size_t smem = sizeof(float) * ((size_t)ATT_PAIRS * a->dim + (size_t)ATT_KEYS * (a->dim + 4) + (size_t)ATT_KEYS * a->vdim + ATT_PAIRS * ATT_KEYS);
   if (smem > 227 * 1024) return THA_STATUS_NOT_SUPPORTED;
   // position tiles: at most one ragged tile per sequence beyond rows / AP
   const dim3 grid(rows->n_rows / AP + rows->n_seqs, a->kv_heads, ceil_div(gsize, AG));

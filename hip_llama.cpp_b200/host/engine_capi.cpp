@@ -56,12 +56,14 @@ extern "C" int thaEngineStep(tha_engine_t* e, int n_entries, const char* const* 
     entries[i].want.assign(wants + w, wants + w + nw);
     w += nw;
   }
-  std::vector<float> logits, taps;
-  if (!e->engine->step(entries, &logits, taps_out ? &taps : nullptr)) return 5;
-  if (logits_out) std::copy(logits.begin(), logits.end(), logits_out);
+  std::vector<float> taps;
+  if (!e->engine->step_pinned(entries, taps_out ? &taps : nullptr)) return 5;
+  if (logits_out) std::copy(e->engine->last_logits(), e->engine->last_logits() + e->engine->last_wanted() * (size_t)e->model->vocab(), logits_out);
   if (taps_out) std::copy(taps.begin(), taps.end(), taps_out);
   return 0;
 }
+extern "C" const float* thaEngineLogits(tha_engine_t* e) { return e->engine->last_logits(); }
+extern "C" long long thaEngineWanted(tha_engine_t* e) { return (long long)e->engine->last_wanted(); }
 extern "C" int thaEngineFinish(tha_engine_t* e, const char* id) { e->engine->finish(id); return 0; }
 
 extern "C" int thaEngineGenerate(tha_engine_t* e, int n_requests, const int* prompt_lens, const int* prompts, const int* max_new,

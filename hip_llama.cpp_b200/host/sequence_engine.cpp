@@ -27,6 +27,7 @@ SequenceEngine::SequenceEngine(LayerModel* model, int max_tokens, int max_seqs)
 SequenceEngine::~SequenceEngine() {
   if (stream_) { tha_stream_sync(stream_); tha_stream_destroy(stream_); }
   if (stage_h_) tha_host_free(stage_h_);
+  if (logits_h_) tha_host_free(logits_h_);
   for (void* p : {(void*)stage_d_, (void*)logits_d_, (void*)taps_d_, (void*)rng_d_, (void*)next_d_, (void*)samp_pos_d_, (void*)reseed_d_})
     if (p) tha_free(p);
 }
@@ -49,7 +50,15 @@ void SequenceEngine::finish(const std::string& id) {
 }
 
 bool SequenceEngine::step(const std::vector<StepEntry>& entries, std::vector<float>* logits, std::vector<float>* taps) {
+  if (!run(entries, logits != nullptr, taps)) return false;
+  if (logits) logits->assign(logits_h_, logits_h_ + last_wanted_ * (size_t)model_->vocab());
+  return true;
+}
+bool SequenceEngine::step_pinned(const std::vector<StepEntry>& entries, std::vector<float>* taps) { return run(entries, true, taps); }
+
+bool SequenceEngine::run(const std::vector<StepEntry>& entries, bool to_host, std::vector<float>* taps) {
   if (!ok_) return false;
+  last_wanted_ = 0;
   const int vocab = model_->vocab();
   // ---- admission and blocks ---------------------------------------------------------------------------------------
   std::vector<const StepEntry*> live;
@@ -78,7 +87,6 @@ bool SequenceEngine::step(const std::vector<StepEntry>& entries, std::vector<flo
     R += e.tokens.size();
     n_want += e.want.size();
   }
-  if (logits) logits->assign(n_want * (size_t)vocab, 0.f);
   if (R == 0) return true;
   // a slot taken in this step was zeroed on the null stream; the engine's stream does not order itself behind that
   if (admitted) tha_stream_sync(nullptr);
@@ -153,7 +161,14 @@ bool SequenceEngine::step(const std::vector<StepEntry>& entries, std::vector<flo
   const int status = tha_hyb_step(stream_, model_->device_model(), &rows, &kv, &st, (int)n_want, want_d, n_want ? logits_d_ : nullptr,
                                   taps ? taps_d_ : nullptr);
   if (status != 0) return fail(std::string("step failed (status ") + std::to_string(status) + "): " + tha_last_error());
-  if (logits && n_want && tha_memcpy_async(logits->data(), logits_d_, n_want * (size_t)vocab * sizeof(float), stream_) != 0) return fail(tha_last_error());
+  if (to_host && n_want) {
+    if (n_want * (size_t)vocab > logits_h_cap_) {
+      if (logits_h_) tha_host_free(logits_h_);
+      logits_h_cap_ = n_want * (size_t)vocab * 2;
+      if (tha_host_alloc((void**)&logits_h_, logits_h_cap_ * sizeof(float)) != 0) { logits_h_ = nullptr; logits_h_cap_ = 0; return fail(tha_last_error()); }
+    }
+    if (tha_memcpy_async(logits_h_, logits_d_, n_want * (size_t)vocab * sizeof(float), stream_) != 0) return fail(tha_last_error());
+  }
   if (taps) {
     taps->resize(n_taps);
     if (tha_memcpy_async(taps->data(), taps_d_, n_taps * sizeof(float), stream_) != 0) return fail(tha_last_error());
@@ -165,6 +180,7 @@ bool SequenceEngine::step(const std::vector<StepEntry>& entries, std::vector<flo
     bm_.logical_KV_table[s].second = filled_[s];
   }
   steps_++;
+  if (to_host) last_wanted_ = n_want;
   return true;
 }
 

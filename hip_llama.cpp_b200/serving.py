@@ -46,6 +46,10 @@ def host_lib():
         lib.thaEngineSlot.argtypes = [vp, C.c_char_p]
         lib.thaEngineStep.argtypes = [vp, I, C.POINTER(C.c_char_p), vp, vp, vp, vp, vp, vp]
         lib.thaEngineFinish.argtypes = [vp, C.c_char_p]
+        lib.thaEngineLogits.argtypes = [vp]
+        lib.thaEngineLogits.restype = C.POINTER(C.c_float)
+        lib.thaEngineWanted.argtypes = [vp]
+        lib.thaEngineWanted.restype = C.c_longlong
         lib.thaEngineGenerate.argtypes = [vp, I, vp, vp, vp, C.c_float, C.c_float, C.c_ulonglong, I, vp]
         _host = lib
     return _host
@@ -80,21 +84,28 @@ class ServingEngine:
         except Exception:
             pass
 
-    def step(self, entries, taps: bool = False):
+    def step(self, entries, taps: bool = False, copy: bool = True):
         """entries: [(id, tokens, want), ...].  Returns logits [wanted, vocab] (and the residual stream after every
-        layer, [layers, rows, width], with taps=True)."""
+        layer, [layers, rows, width], with taps=True).  copy=False returns a view of the engine's pinned buffer that the
+        next step overwrites."""
         n = len(entries)
         ids = (C.c_char_p * n)(*[e[0].encode() for e in entries])
         counts = np.array([len(e[1]) for e in entries], np.int32)
         tokens = np.array([t for e in entries for t in e[1]], np.int32)
         wc = np.array([len(e[2]) for e in entries], np.int32)
         wants = np.array([w for e in entries for w in e[2]], np.int32)
-        logits = np.zeros((int(wc.sum()), self.vocab), np.float32)
+        nw = int(wc.sum())
         tp = np.zeros((self.layers, int(counts.sum()), self.width), np.float32) if taps else None
         st = self.lib.thaEngineStep(self.h, n, ids, counts.ctypes.data, tokens.ctypes.data, wc.ctypes.data, wants.ctypes.data,
-                                    logits.ctypes.data, tp.ctypes.data if taps else None)
+                                    None, tp.ctypes.data if taps else None)
         if st != 0:
             raise ServingError(self.lib.thaEngineError(self.h).decode())
+        if nw:
+            logits = np.ctypeslib.as_array(self.lib.thaEngineLogits(self.h), shape=(nw, self.vocab))
+            if copy:
+                logits = logits.copy()
+        else:
+            logits = np.zeros((0, self.vocab), np.float32)
         return (logits, tp) if taps else logits
 
     def finish(self, rid: str):

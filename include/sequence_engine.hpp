@@ -44,6 +44,11 @@ class SequenceEngine {
   // One step.  logits: [sum of wants, vocab] in entry order (may be NULL when nothing is wanted); taps (optional):
   // the residual stream after every layer, [layers, rows, width].
   bool step(const std::vector<StepEntry>& entries, std::vector<float>* logits, std::vector<float>* taps = nullptr);
+  // The same step with the wanted logits left in the engine's pinned host buffer (no second copy): last_logits() is
+  // [last_wanted(), vocab] and stays valid until the next step.
+  bool step_pinned(const std::vector<StepEntry>& entries, std::vector<float>* taps = nullptr);
+  const float* last_logits() const { return logits_h_; }
+  size_t last_wanted() const { return last_wanted_; }
   // the request is finished: its blocks and its slot go back
   void finish(const std::string& id);
   int live() const { return (int)slot_of_.size(); }
@@ -69,7 +74,9 @@ class SequenceEngine {
   int next_request_id_ = 0;
   // staging: one pinned host block and one device block for the row arrays, regrown on demand
   int* stage_h_ = nullptr; int* stage_d_ = nullptr; size_t stage_cap_ = 0;
+  bool run(const std::vector<StepEntry>& entries, bool to_host, std::vector<float>* taps);
   float* logits_d_ = nullptr; size_t logits_cap_ = 0;
+  float* logits_h_ = nullptr; size_t logits_h_cap_ = 0; size_t last_wanted_ = 0;
   float* taps_d_ = nullptr; size_t taps_cap_ = 0;
   // samplers
   unsigned long long* rng_d_ = nullptr; int* next_d_ = nullptr; int* samp_pos_d_ = nullptr; unsigned long long* reseed_d_ = nullptr;

@@ -25,6 +25,10 @@ int thaEngineSlot(tha_engine_t* e, const char* id); /* -1: not live */
  * taps_out (nullable): residual stream after every layer, [layers, rows, width]. */
 int thaEngineStep(tha_engine_t* e, int n_entries, const char* const* ids, const int* counts, const int* tokens,
                   const int* want_counts, const int* wants, float* logits_out, float* taps_out);
+/* the logits of the last step in the engine's pinned host buffer, [thaEngineWanted, vocab]; valid until the next step
+ * (pass logits_out = NULL to thaEngineStep to skip the copy into a caller's buffer) */
+const float* thaEngineLogits(tha_engine_t* e);
+long long thaEngineWanted(tha_engine_t* e);
 int thaEngineFinish(tha_engine_t* e, const char* id);
 /* Generation through the scheduler: request i has prompt_lens[i] prompt tokens (consecutive in `prompts`) and gets
  * max_new[i] tokens, written consecutively to out_tokens.  temperature 0 = greedy. */

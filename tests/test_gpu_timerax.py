@@ -396,3 +396,21 @@ def test_plain_products_everywhere(general, monkeypatch):
     toks = tokens_for(general, 60, 14)
     z, _ = general.ref(toks)
     assert rel_err(feed(general.engine("bfloat16"), "a", toks, [60]), z) < BF16_TOL
+
+
+def test_the_app_serves_a_model_folder(general, tmp_path):
+    """build/apps/llama on a folder: the registry picks the design, requests are lines of token ids."""
+    import os
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    app = os.path.join(root, "build", "apps", "llama")
+    if not os.path.exists(app):
+        pytest.skip("the app is not built")
+    prompts = [tokens_for(general, n, 80 + n) for n in (4, 19, 33)]
+    (tmp_path / "in.txt").write_text("\n".join(" ".join(map(str, p)) for p in prompts) + "\n")
+    r = subprocess.run([app, general.folder, "-m", "test", "-f", str(tmp_path / "in.txt"), "-o", str(tmp_path / "out.txt"), "-n", "7", "-b", "2",
+                        "-d", "f32", "-j", "16"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    got = [[int(t) for t in line.split()] for line in (tmp_path / "out.txt").read_text().splitlines()]
+    want = general.engine(max_seqs=2).generate(prompts, [7, 7, 7], temperature=0.0, portion=16)
+    assert got == want
