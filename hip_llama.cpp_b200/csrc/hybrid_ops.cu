@@ -290,7 +290,7 @@ constexpr int ATT_PAIRS = 16, ATT_KEYS = 32, ATT_MAX_VC = 8;   // value channels
 
 template <typename T>
 __global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t rows, tha_kv_t kv, const float* __restrict__ q,
-                                                       T* __restrict__ out, int AG, int AP) {
+                                                       T* __restrict__ out, int AG, int AP, int splits, float* __restrict__ partial) {
   extern __shared__ __align__(16) float sm[];
   const int D = a.dim, E = a.vdim, gsize = a.heads / a.kv_heads;
   const bool vec = ((D | E) & 3) == 0;         // 128-bit shared-memory reads: rows padded to keep them aligned and conflict-free
@@ -302,7 +302,7 @@ __global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t 
   // which sequence and which positions: tiles of AP rows per sequence, found by walking the sequences
   int seq = -1, r0 = 0, r_end = 0;
   {
-    int tile = blockIdx.x;
+    int tile = blockIdx.x / splits;
     for (int s = 0; s < rows.n_seqs; s++) {
       const int lo = rows.seq_first[s], hi = rows.seq_first[s + 1];
       const int nt = (hi - lo + AP - 1) / AP;
@@ -336,7 +336,15 @@ __global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t 
     for (int c = 0; c < ATT_MAX_VC; c++) acc[rr][c] = 0.f;
   }
   const int key_lo = a.chunk > 0 ? (p_first / a.chunk) * a.chunk : 0;
-  for (int kt = (key_lo / ATT_KEYS) * ATT_KEYS; kt <= p_last; kt += ATT_KEYS) {
+  // with splits > 1 (few rows, long contexts) the key tiles are dealt to `splits` blocks in contiguous runs; each leaves
+  // its running (max, sum, accumulator) in `partial` and hyb_attn_merge_kernel combines them in order
+  int kt_begin = (key_lo / ATT_KEYS) * ATT_KEYS, kt_last = p_last;
+  if (splits > 1) {
+    const int n_kt = (p_last - kt_begin) / ATT_KEYS + 1, per = (n_kt + splits - 1) / splits, sp = blockIdx.x % splits;
+    kt_last = min(p_last, kt_begin + (sp + 1) * per * ATT_KEYS - 1);
+    kt_begin += sp * per * ATT_KEYS;
+  }
+  for (int kt = kt_begin; kt <= kt_last; kt += ATT_KEYS) {
     __syncthreads();   // the previous tile is consumed (and Qs is written, the first time)
     // a warp fetches 8 keys: all 8 table entries first, then the rows four at a time into registers before any of them
     // goes to shared memory, so that the loads are in flight together (a load followed by its own store waits for it)
@@ -462,12 +470,40 @@ __global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t 
     if (!my_ok[rr]) continue;
     const int pr = warp * 4 + rr;
     const int r = r0 + pr / AG, h = g * gsize + part * AG + pr % AG;
+    if (splits > 1) {
+      float* dst = partial + (((size_t)(blockIdx.x % splits) * rows.n_rows + r) * a.heads + h) * (E + 2);
+#pragma unroll
+      for (int c = 0; c < ATT_MAX_VC; c++) {
+        const int e = lane + 32 * c;
+        if (e < E) dst[e] = acc[rr][c];
+      }
+      if (lane == 0) { dst[E] = m_run[rr]; dst[E + 1] = l_run[rr]; }
+      continue;
+    }
     const float inv = 1.0f / l_run[rr];
 #pragma unroll
     for (int c = 0; c < ATT_MAX_VC; c++) {
       const int e = lane + 32 * c;
       if (e < E) hyb_store(out + (size_t)r * a.heads * E + (size_t)h * E + e, acc[rr][c] * inv);
     }
+  }
+}
+
+// the splits of a (row, head) in ascending key order: out = sum_s acc_s e^(m_s - M) / sum_s l_s e^(m_s - M); a warp each
+template <typename T>
+__global__ void hyb_attn_merge_kernel(T* __restrict__ out, const float* __restrict__ partial, int n_rows, int heads, int E, int splits) {
+  const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (idx >= n_rows * heads) return;
+  const size_t stride = (size_t)n_rows * heads * (E + 2);
+  const float* p0 = partial + (size_t)idx * (E + 2);
+  float M = -INFINITY;
+  for (int s = 0; s < splits; s++) M = fmaxf(M, p0[s * stride + E]);
+  float L = 0.f;
+  for (int s = 0; s < splits; s++) { const float ms = p0[s * stride + E]; if (ms > -INFINITY) L += p0[s * stride + E + 1] * expf(ms - M); }
+  for (int e = lane; e < E; e += 32) {
+    float o = 0.f;
+    for (int s = 0; s < splits; s++) { const float ms = p0[s * stride + E]; if (ms > -INFINITY) o = fmaf(p0[s * stride + e], expf(ms - M), o); }
+    hyb_store(out + (size_t)idx * E + e, o / L);
   }
 }
 
@@ -1019,7 +1055,7 @@ extern "C" int tha_hyb_attn_prepare(void* stream, const tha_attn_t* a, const tha
 }
 
 extern "C" int tha_hyb_attn(void* stream, int dtype, const tha_attn_t* a, const tha_rows_t* rows, const tha_kv_t* kv, const float* q,
-                            void* out) {
+                            void* out, float* split_scratch, size_t split_scratch_floats) {
   if (rows->n_rows < 1) return THA_STATUS_SUCCESS;
   if (a->heads % a->kv_heads || a->vdim > 32 * ATT_MAX_VC) return THA_STATUS_NOT_SUPPORTED;
   const int gsize = a->heads / a->kv_heads;
@@ -1027,14 +1063,31 @@ extern "C" int tha_hyb_attn(void* stream, int dtype, const tha_attn_t* a, const 
   const size_t smem = sizeof(float) * ((size_t)ATT_PAIRS * a->dim + (size_t)ATT_KEYS * (a->dim + 4) + (size_t)ATT_KEYS * a->vdim + ATT_PAIRS * ATT_KEYS);
   if (smem > 227 * 1024) return THA_STATUS_NOT_SUPPORTED;
   // position tiles: at most one ragged tile per sequence beyond rows / AP
-  const dim3 grid(rows->n_rows / AP + rows->n_seqs, a->kv_heads, ceil_div(gsize, AG));
+  const int tiles = rows->n_rows / AP + rows->n_seqs;
+  // few blocks and many keys (decoding at long contexts): deal the key tiles of a block to several
+  const int seen = rows->max_pos + 1, max_keys = a->chunk > 0 && a->chunk < seen ? a->chunk : seen;
+  int splits = 1;
+  const long long blocks = (long long)tiles * a->kv_heads * ceil_div(gsize, AG);
+  if (split_scratch && blocks < 4 * 148 && max_keys >= 4 * ATT_KEYS) {
+    splits = (int)((6 * 148 + blocks - 1) / blocks);
+    if (splits > max_keys / (2 * ATT_KEYS)) splits = max_keys / (2 * ATT_KEYS);
+    if (splits > 16) splits = 16;
+    while (splits > 1 && (size_t)splits * rows->n_rows * a->heads * (a->vdim + 2) > split_scratch_floats) splits--;
+  }
+  const dim3 grid(tiles * splits, a->kv_heads, ceil_div(gsize, AG));
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == THA_DT_BF16) {
     if (smem > 48 * 1024) THA_CUDA_OK(cudaFuncSetAttribute(hyb_attn_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    THA_CUDA_OK(launch(hyb_attn_kernel<bf16>, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, (bf16*)out, AG, AP));
+    THA_CUDA_OK(launch(hyb_attn_kernel<bf16>, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, (bf16*)out, AG, AP, splits, split_scratch));
+    if (splits > 1)
+      THA_CUDA_OK(launch(hyb_attn_merge_kernel<bf16>, dim3(ceil_div(rows->n_rows * a->heads, 4)), dim3(128), 0, s, false, (bf16*)out,
+                         (const float*)split_scratch, rows->n_rows, a->heads, a->vdim, splits));
   } else {
     if (smem > 48 * 1024) THA_CUDA_OK(cudaFuncSetAttribute(hyb_attn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    THA_CUDA_OK(launch(hyb_attn_kernel<float>, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, (float*)out, AG, AP));
+    THA_CUDA_OK(launch(hyb_attn_kernel<float>, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, (float*)out, AG, AP, splits, split_scratch));
+    if (splits > 1)
+      THA_CUDA_OK(launch(hyb_attn_merge_kernel<float>, dim3(ceil_div(rows->n_rows * a->heads, 4)), dim3(128), 0, s, false, (float*)out,
+                         (const float*)split_scratch, rows->n_rows, a->heads, a->vdim, splits));
   }
   return THA_STATUS_SUCCESS;
 }

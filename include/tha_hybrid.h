@@ -176,9 +176,11 @@ int tha_hyb_rotary_table(void* stream, const tha_rotary_t* rot, const int* pos, 
 /* rotate q and k, unit-rms them, write k and v to the cache rows of (slot, pos), q to q_out [n_rows, heads * dim] */
 int tha_hyb_attn_prepare(void* stream, const tha_attn_t* a, const tha_rows_t* rows, const tha_kv_t* kv, const float* proj,
                          long long ldp, const float* cos_t, const float* sin_t, int rot_dims, float* q_out);
-/* softmax attention of every row over its visible cache rows; out dtype-typed [n_rows, heads * vdim] */
+/* softmax attention of every row over its visible cache rows; out dtype-typed [n_rows, heads * vdim].
+ * split_scratch (nullable, fp32): room for the partial results when a step of few rows at long contexts is cut along
+ * the keys (splits * n_rows * heads * (vdim + 2) floats are used, as many splits as fit, at most 16) */
 int tha_hyb_attn(void* stream, int dtype, const tha_attn_t* a, const tha_rows_t* rows, const tha_kv_t* kv, const float* q,
-                 void* out);
+                 void* out, float* split_scratch, size_t split_scratch_floats);
 /* the matrix memory over the rows of every sequence in order, state read from and written back to the slots;
  * o_raw: fp32 scratch [n_rows, heads * vdim] (the read-out before the head norm);
  * out dtype-typed [n_rows, heads * vdim] = unit-rms per head * norm * sigmoid(gate) */

@@ -414,3 +414,22 @@ def test_the_app_serves_a_model_folder(general, tmp_path):
     got = [[int(t) for t in line.split()] for line in (tmp_path / "out.txt").read_text().splitlines()]
     want = general.engine(max_seqs=2).generate(prompts, [7, 7, 7], temperature=0.0, portion=16)
     assert got == want
+
+
+def test_prompt_sized_step_runs_the_experts_one_matmul_each(tmp_path, monkeypatch):
+    """From 1024 rows a bfloat16 step may gather the rows into expert order and give each expert to the tensor-core matmul
+    (it does when experts get many rows each; the switch lowers that bar to the test's size)."""
+    monkeypatch.setenv("THA_HYB_EXPERT_ROWS", "100")
+    cfg = model_cfg([parallel_cfg(moe_cfg(experts=5, top=2, ff=64, shared=64), heads=2, kv_heads=1, dim=32, vdim=32, chunk=128, rot_dims=32,
+                                  mheads=2, mdim=32, mvdim=32),
+                     delta_cfg(moe_cfg(experts=3, top=1, ff=72, shared=0), heads=2, kv_heads=1, dim=32, vdim=32)], width=64, vocab=90)
+    b = Built(tmp_path, cfg, 31)
+    toks = tokens_for(b, 1100, 9)
+    z, _ = b.ref(toks)
+    e = b.engine("bfloat16", max_tokens=1152)
+    got = e.step([("a", toks, list(range(0, 1100, 7)))])
+    assert rel_err(got, z[::7]) < BF16_TOL
+    small = b.engine("bfloat16", max_tokens=1152)          # the same prompt in small steps: the grouped kernel
+    got2 = feed(small, "a", toks, [500])[::7]
+    assert rel_err(got2, z[::7]) < BF16_TOL
+    assert rel_err(got2, got) < BF16_TOL / 2
