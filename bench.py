@@ -61,6 +61,7 @@ def parse_args():
     ap.add_argument("--design-sizes", default="w1024,w2048")
     ap.add_argument("--design-prompt", type=int, default=4096)
     ap.add_argument("--design-batch", type=int, default=64)
+    ap.add_argument("--design-only", action="store_true", help="with --design: skip the llama2 arm")
     ap.add_argument("--kernels", action="store_true", help="with --design: print the per-kernel timeline of one prompt step and one "
                     "decode step (slower: an event after every launch) and skip the llama2 arm")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -771,7 +772,7 @@ def main():
         from pkgload import load_pkg
         bd = load_pkg("bench_designs")
         res = bd.run(load_pkg, args.design_sizes.split(","), prompt_len=args.design_prompt, batch=args.design_batch, steps=max(4, min(args.steps, 32)),
-                     warmup=max(3, min(args.warmup, 8)), kernels=args.kernels, llama=not args.kernels)
+                     warmup=max(3, min(args.warmup, 8)), kernels=args.kernels, llama=not (args.kernels or args.design_only))
         print(json.dumps({"design": args.design, "dtype": "bf16", "data": "synthetic (random weights)", "n_gpus": 1,
                           "timing": "wall clock around the engine's step call (rows up, wanted logits back, stream synchronised), median",
                           "sizes": res}))

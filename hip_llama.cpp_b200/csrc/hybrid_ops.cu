@@ -603,7 +603,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) hyb_mem_scan_kernel(tha_mem_t m,
 // The same two recurrences with the state in REGISTERS, for head sizes up to 256 key channels: a warp owns SCW value
 // columns, lane l the key channels l, l + 32, ... of those columns.  Nothing is shared between warps, so a token costs no
 // block barrier: the column sums S^T q (and S^T k) are warp shuffles, the next token's inputs are fetched a token ahead.
-constexpr int SCW = 2, SCAN_WARPS = 4;
+constexpr int SCW = 2, SCAN_WARPS = 4, SCAN_AHEAD = 4;
 
 template <int RPL>
 __global__ void __launch_bounds__(32 * SCAN_WARPS) hyb_mem_scan_warp_kernel(tha_mem_t m, tha_rows_t rows, tha_state_store_t st,
@@ -625,31 +625,37 @@ __global__ void __launch_bounds__(32 * SCAN_WARPS) hyb_mem_scan_warp_kernel(tha_
   float mrun = gstate[(size_t)D * E + D];
   const float qscale = 1.0f / sqrtf((float)D);
   const int r_begin = rows.seq_first[s], r_end = rows.seq_first[s + 1];
-  float q[RPL], k[RPL], v[SCW], gi = 0.f, gf = 0.f;
-  auto fetch = [&](int r) {
+  // a token's inputs are loaded SCAN_AHEAD tokens before they are used (a ring of register sets, the loop unrolled over
+  // it), so that a load has several tokens' worth of arithmetic to arrive in
+  struct In { float q[RPL], k[RPL], v[SCW], gi, gf; };
+  In ring[SCAN_AHEAD];
+  auto fetch = [&](int r, In& in) {
     const float* pr = proj + (size_t)r * ldp;
 #pragma unroll
     for (int i = 0; i < RPL; i++) {
       const int d = lane + 32 * i;
-      q[i] = d < D ? pr[m.o_q + h * D + d] : 0.f;
-      k[i] = d < D ? pr[m.o_k + h * D + d] : 0.f;
+      in.q[i] = d < D ? pr[m.o_q + h * D + d] : 0.f;
+      in.k[i] = d < D ? pr[m.o_k + h * D + d] : 0.f;
     }
 #pragma unroll
-    for (int c = 0; c < SCW; c++) v[c] = e0 + c < E ? pr[m.o_v + h * E + e0 + c] : 0.f;
-    gi = pr[m.o_i + h];
-    gf = pr[m.o_f + h];
+    for (int c = 0; c < SCW; c++) in.v[c] = e0 + c < E ? pr[m.o_v + h * E + e0 + c] : 0.f;
+    in.gi = pr[m.o_i + h];
+    in.gf = pr[m.o_f + h];
   };
-  if (r_begin < r_end) fetch(r_begin);
+#pragma unroll
+  for (int u = 0; u < SCAN_AHEAD; u++)
+    if (r_begin + u < r_end) fetch(r_begin + u, ring[u]);
   const float bi = m.b_i[h], bf = m.b_f[h];
-  for (int r = r_begin; r < r_end; r++) {
+  // one token; `refill` (a row, or -1) is what the token's ring entry is loaded with once its values are taken
+  auto token = [&](int r, In& in, int refill) {
     float cq[RPL], ck[RPL], cv[SCW];
 #pragma unroll
-    for (int i = 0; i < RPL; i++) { cq[i] = q[i] * qscale; ck[i] = k[i]; }
+    for (int i = 0; i < RPL; i++) { cq[i] = in.q[i] * qscale; ck[i] = in.k[i]; }
 #pragma unroll
-    for (int c = 0; c < SCW; c++) cv[c] = v[c];
-    const float ig = hyb_softcap(gi + bi, m.gate_cap);
-    const float fg = hyb_logsigmoid(hyb_softcap(gf + bf, m.gate_cap));
-    if (r + 1 < r_end) fetch(r + 1);
+    for (int c = 0; c < SCW; c++) cv[c] = in.v[c];
+    const float ig = hyb_softcap(in.gi + bi, m.gate_cap);
+    const float fg = hyb_logsigmoid(hyb_softcap(in.gf + bf, m.gate_cap));
+    if (refill >= 0) fetch(refill, in);
     const float mnew = fmaxf(fg + mrun, ig);
     const float a = expf(fg + mrun - mnew), b = expf(ig - mnew);
     mrun = mnew;
@@ -667,13 +673,23 @@ __global__ void __launch_bounds__(32 * SCAN_WARPS) hyb_mem_scan_warp_kernel(tha_
       }
     }
     nq = warp_sum(nq);
-    const float den = fmaxf(fabsf(nq), expf(-mrun)) + 1e-6f;
+    const float den = fmaxf(fabsf(nq), expf(-mnew)) + 1e-6f;
 #pragma unroll
     for (int c = 0; c < SCW; c++) {
       const float o = warp_sum(acc[c]);
       if (lane == c && e0 + c < E) o_raw[(size_t)r * m.heads * E + (size_t)h * E + e0 + c] = o / den;
     }
+  };
+  // whole groups without a branch between their tokens (the refill row is clamped instead of tested), so that one
+  // token's shuffles and stores can be scheduled under the next token's arithmetic; then the ragged end
+  int rb = r_begin;
+  for (; rb + SCAN_AHEAD <= r_end; rb += SCAN_AHEAD) {
+#pragma unroll
+    for (int u = 0; u < SCAN_AHEAD; u++) token(rb + u, ring[u], min(rb + u + SCAN_AHEAD, r_end - 1));
   }
+#pragma unroll
+  for (int u = 0; u < SCAN_AHEAD; u++)
+    if (rb + u < r_end) token(rb + u, ring[u], -1);
 #pragma unroll
   for (int i = 0; i < RPL; i++) {
     const int d = lane + 32 * i;
