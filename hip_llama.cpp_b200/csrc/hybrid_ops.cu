@@ -510,10 +510,33 @@ __global__ void hyb_attn_merge_kernel(T* __restrict__ out, const float* __restri
 // ------------------------------------------------------------------------------------------------------------------
 // matrix memory: one block per (sequence, head); S [dim, vdim], n [dim] in shared memory, tokens in order.
 // ------------------------------------------------------------------------------------------------------------------
+
 __device__ __forceinline__ float hyb_softcap(float z, float cap) { return cap * tanhf(z / cap); }
 __device__ __forceinline__ float hyb_logsigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
 __device__ __forceinline__ float hyb_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float hyb_softplus(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
+
+// The scalar arithmetic of the gates does not depend on the state, so it runs for all rows at once before the scans and
+// in place: the two gate columns of the stacked projection become the log input gate cap * tanh((z + b) / cap) and the log
+// forget gate logsigmoid(cap * tanh((z + b) / cap)); for the delta rule the raw step sizes become the decays
+// exp(-exp(A_log) * softplus(z + dt_bias)) and the raw write strength becomes sigmoid(z).
+__global__ void hyb_mem_gates_kernel(float* __restrict__ proj, long long ldp, int n_rows, int heads, int o_i, int o_f,
+                                     const float* __restrict__ b_i, const float* __restrict__ b_f, float cap) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n_rows * heads) return;
+  const int r = idx / heads, h = idx - r * heads;
+  float* pr = proj + (size_t)r * ldp;
+  pr[o_i + h] = hyb_softcap(pr[o_i + h] + b_i[h], cap);
+  pr[o_f + h] = hyb_logsigmoid(hyb_softcap(pr[o_f + h] + b_f[h], cap));
+}
+__global__ void hyb_delta_gates_kernel(float* __restrict__ dt, float* __restrict__ proj, long long ldp, int n_rows, int heads, int D, int o_b,
+                                       const float* __restrict__ a_log, const float* __restrict__ dt_bias) {
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (size_t)n_rows * heads * D) return;
+  const int hd = (int)(idx % ((size_t)heads * D)), h = hd / D;
+  dt[idx] = expf(-expf(a_log[h]) * hyb_softplus(dt[idx] + dt_bias[hd]));
+  if (hd % D == 0) { float* b = proj + (idx / ((size_t)heads * D)) * ldp + o_b + h; *b = hyb_sigmoid(*b); }
+}
 
 // The state's value columns are independent of each other (column e of S only ever meets v[e]), so a head is cut into
 // slices of SC columns, one block each: block (sequence, head, slice) keeps S[:, slice] in shared memory, its own copy of
@@ -548,7 +571,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) hyb_mem_scan_kernel(tha_mem_t m,
     if (i < D) return pr[m.o_q + h * D + i] * qscale;
     if (i < 2 * D) return pr[m.o_k + h * D + (i - D)];
     if (i < 2 * D + SC) return (i - 2 * D) < ec ? pr[m.o_v + h * E + e0 + (i - 2 * D)] : 0.f;
-    return i == 2 * D + SC ? pr[m.o_i + h] + m.b_i[h] : pr[m.o_f + h] + m.b_f[h];
+    return i == 2 * D + SC ? pr[m.o_i + h] : pr[m.o_f + h];   // the log gates (hyb_mem_gates_kernel)
   };
   constexpr int PF = 4;             // prefetch registers per thread: up to 1024 inputs per token
   float pf[PF];
@@ -566,8 +589,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) hyb_mem_scan_kernel(tha_mem_t m,
     }
     __syncthreads();
     const float* sq = cur; const float* sk = cur + D; const float* sv = cur + 2 * D;
-    const float ig = hyb_softcap(cur[2 * D + SC], m.gate_cap);
-    const float fg = hyb_logsigmoid(hyb_softcap(cur[2 * D + SC + 1], m.gate_cap));
+    const float ig = cur[2 * D + SC], fg = cur[2 * D + SC + 1];
     const float mnew = fmaxf(fg + mrun, ig);
     const float a = expf(fg + mrun - mnew), b = expf(ig - mnew);
     mrun = mnew;
@@ -645,7 +667,6 @@ __global__ void __launch_bounds__(32 * SCAN_WARPS) hyb_mem_scan_warp_kernel(tha_
 #pragma unroll
   for (int u = 0; u < SCAN_AHEAD; u++)
     if (r_begin + u < r_end) fetch(r_begin + u, ring[u]);
-  const float bi = m.b_i[h], bf = m.b_f[h];
   // one token; `refill` (a row, or -1) is what the token's ring entry is loaded with once its values are taken
   auto token = [&](int r, In& in, int refill) {
     float cq[RPL], ck[RPL], cv[SCW];
@@ -653,8 +674,7 @@ __global__ void __launch_bounds__(32 * SCAN_WARPS) hyb_mem_scan_warp_kernel(tha_
     for (int i = 0; i < RPL; i++) { cq[i] = in.q[i] * qscale; ck[i] = in.k[i]; }
 #pragma unroll
     for (int c = 0; c < SCW; c++) cv[c] = in.v[c];
-    const float ig = hyb_softcap(in.gi + bi, m.gate_cap);
-    const float fg = hyb_logsigmoid(hyb_softcap(in.gf + bf, m.gate_cap));
+    const float ig = in.gi, fg = in.gf;   // the log gates (hyb_mem_gates_kernel)
     if (refill >= 0) fetch(refill, in);
     const float mnew = fmaxf(fg + mrun, ig);
     const float a = expf(fg + mrun - mnew), b = expf(ig - mnew);
@@ -714,15 +734,13 @@ __global__ void __launch_bounds__(32 * SCAN_WARPS) hyb_delta_scan_warp_kernel(th
   const int hk = h / (dl.heads / dl.kv_heads);
   const int C = 2 * dl.kv_heads * D + dl.heads * E;
   float* gstate = st.base + (size_t)rows.seq_slot[s] * st.slot_floats + dl.state_off + (size_t)h * D * E;
-  float S[RPL][SCW], bias[RPL];
+  float S[RPL][SCW];
 #pragma unroll
   for (int i = 0; i < RPL; i++) {
     const int d = lane + 32 * i;
-    bias[i] = d < D ? dl.dt_bias[h * D + d] : 0.f;
 #pragma unroll
     for (int c = 0; c < SCW; c++) S[i][c] = (d < D && e0 + c < E) ? gstate[(size_t)d * E + e0 + c] : 0.f;
   }
-  const float decay_rate = expf(dl.a_log[h]);
   const float qscale = 1.0f / sqrtf((float)D);
   const int r_begin = rows.seq_first[s], r_end = rows.seq_first[s + 1];
   float q[RPL], k[RPL], dt[RPL], v[SCW], braw = 0.f;
@@ -748,11 +766,11 @@ __global__ void __launch_bounds__(32 * SCAN_WARPS) hyb_delta_scan_warp_kernel(th
       cq[i] = q[i]; ck[i] = k[i];
       qq = fmaf(cq[i], cq[i], qq);
       kk = fmaf(ck[i], ck[i], kk);
-      cg[i] = expf(-decay_rate * hyb_softplus(dt[i] + bias[i]));   // lanes past D hold S = 0, whatever their decay
+      cg[i] = dt[i];   // the decay (hyb_delta_gates_kernel); lanes past D hold S = 0 whatever it is
     }
 #pragma unroll
     for (int c = 0; c < SCW; c++) cv[c] = v[c];
-    const float beta = hyb_sigmoid(braw);
+    const float beta = braw;
     if (r + 1 < r_end) fetch(r + 1);
     qq = warp_sum(qq);
     kk = warp_sum(kk);
@@ -860,16 +878,15 @@ __global__ void __launch_bounds__(SCAN_THREADS) hyb_delta_scan_kernel(tha_delta_
   float* su = part + parts * SC;     // [SC]
   float* gstate = st.base + (size_t)rows.seq_slot[s] * st.slot_floats + dl.state_off + (size_t)h * D * E;
   for (int i = threadIdx.x; i < D * SC; i += nt) { const int d = i / SC, e = i - d * SC; S[i] = e < ec ? gstate[(size_t)d * E + e0 + e] : 0.f; }
-  const float decay_rate = expf(dl.a_log[h]);
   const float qscale = 1.0f / sqrtf((float)D);
   const int r_begin = rows.seq_first[s], r_end = rows.seq_first[s + 1];
   auto fetch = [&](int r, int i) -> float {
     const float* x = qkv + (size_t)r * C;
     if (i < D) return x[hk * D + i];
     if (i < 2 * D) return x[dl.kv_heads * D + hk * D + (i - D)];
-    if (i < 3 * D) { const int d = i - 2 * D; return expf(-decay_rate * hyb_softplus(dt_raw[(size_t)r * dl.heads * D + h * D + d] + dl.dt_bias[h * D + d])); }
+    if (i < 3 * D) return dt_raw[(size_t)r * dl.heads * D + h * D + (i - 2 * D)];   // the decays (hyb_delta_gates_kernel)
     if (i < 3 * D + SC) return (i - 3 * D) < ec ? x[2 * dl.kv_heads * D + h * E + e0 + (i - 3 * D)] : 0.f;
-    return hyb_sigmoid(proj[(size_t)r * ldp + dl.o_b + h]);
+    return proj[(size_t)r * ldp + dl.o_b + h];
   };
   constexpr int PF = 4;
   float pf[PF];
@@ -1125,9 +1142,11 @@ static int head_gate_launch(cudaStream_t s, T* out, const float* o_raw, int n_ro
 }
 
 extern "C" int tha_hyb_mem_scan(void* stream, int dtype, const tha_mem_t* m, const tha_rows_t* rows, const tha_state_store_t* st,
-                                const float* proj, long long ldp, float* o_raw, void* out) {
+                                float* proj, long long ldp, float* o_raw, void* out) {
   if (rows->n_seqs < 1) return THA_STATUS_SUCCESS;
   cudaStream_t s = (cudaStream_t)stream;
+  THA_CUDA_OK(launch(hyb_mem_gates_kernel, dim3(ceil_div(rows->n_rows * m->heads, 128)), dim3(128), 0, s, false, proj, ldp, rows->n_rows, m->heads,
+                     m->o_i, m->o_f, m->b_i, m->b_f, m->gate_cap));
   if (m->dim <= 256 && scan_in_registers()) {
     const dim3 grid(rows->n_seqs, m->heads, ceil_div(m->vdim, SCW * SCAN_WARPS)), block(32 * SCAN_WARPS);
     if (m->dim <= 32) THA_CUDA_OK(launch(hyb_mem_scan_warp_kernel<1>, grid, block, 0, s, false, *m, *rows, *st, proj, ldp, o_raw));
@@ -1161,11 +1180,16 @@ extern "C" int tha_hyb_conv_silu(void* stream, const tha_rows_t* rows, const tha
 }
 
 extern "C" int tha_hyb_delta_scan(void* stream, int dtype, const tha_delta_t* d, const tha_rows_t* rows, const tha_state_store_t* st,
-                                  const float* qkv, const float* proj, long long ldp, const float* dt_raw, const float* gate_raw,
+                                  const float* qkv, float* proj, long long ldp, float* dt_raw, const float* gate_raw,
                                   float* o_raw, void* out) {
   if (rows->n_seqs < 1) return THA_STATUS_SUCCESS;
   if (d->heads % d->kv_heads) return THA_STATUS_INVALID_ARG;
   cudaStream_t s = (cudaStream_t)stream;
+  {
+    const size_t n = (size_t)rows->n_rows * d->heads * d->dim;
+    THA_CUDA_OK(launch(hyb_delta_gates_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, false, dt_raw, proj, ldp, rows->n_rows, d->heads,
+                       d->dim, d->o_b, d->a_log, d->dt_bias));
+  }
   if (d->dim <= 256 && scan_in_registers()) {
     const dim3 grid(rows->n_seqs, d->heads, ceil_div(d->vdim, SCW * SCAN_WARPS)), block(32 * SCAN_WARPS);
     if (d->dim <= 32) THA_CUDA_OK(launch(hyb_delta_scan_warp_kernel<1>, grid, block, 0, s, false, *d, *rows, *st, qkv, proj, ldp, dt_raw, o_raw));

@@ -182,18 +182,20 @@ int tha_hyb_attn_prepare(void* stream, const tha_attn_t* a, const tha_rows_t* ro
 int tha_hyb_attn(void* stream, int dtype, const tha_attn_t* a, const tha_rows_t* rows, const tha_kv_t* kv, const float* q,
                  void* out, float* split_scratch, size_t split_scratch_floats);
 /* the matrix memory over the rows of every sequence in order, state read from and written back to the slots;
+ * the two gate columns of proj are replaced by the log gates (a pass over all rows before the scan);
  * o_raw: fp32 scratch [n_rows, heads * vdim] (the read-out before the head norm);
  * out dtype-typed [n_rows, heads * vdim] = unit-rms per head * norm * sigmoid(gate) */
 int tha_hyb_mem_scan(void* stream, int dtype, const tha_mem_t* m, const tha_rows_t* rows, const tha_state_store_t* st,
-                     const float* proj, long long ldp, float* o_raw, void* out);
+                     float* proj, long long ldp, float* o_raw, void* out);
 /* causal convolution + silu over `channels` adjacent columns of proj starting at col0, continuing from the slot's
  * tail; out fp32 [n_rows, channels]; then the tails are advanced */
 int tha_hyb_conv_silu(void* stream, const tha_rows_t* rows, const tha_state_store_t* st, long long conv_state_off,
                       const float* proj, long long ldp, int col0, int channels, int taps, const float* w, float* out);
 /* the gated delta rule over the rows of every sequence in order; qkv = the convolved q | k | v, dt_raw [n_rows, heads*dim]
- * and gate_raw [n_rows, heads*vdim] the outputs of the two low-rank projections (before bias / softplus / sigmoid) */
+ * and gate_raw [n_rows, heads*vdim] the outputs of the two low-rank projections (before bias / softplus / sigmoid);
+ * dt_raw is replaced by the decays and the write-strength column of proj by its sigmoid before the scan */
 int tha_hyb_delta_scan(void* stream, int dtype, const tha_delta_t* d, const tha_rows_t* rows, const tha_state_store_t* st,
-                       const float* qkv, const float* proj, long long ldp, const float* dt_raw, const float* gate_raw,
+                       const float* qkv, float* proj, long long ldp, float* dt_raw, const float* gate_raw,
                        float* o_raw, void* out);
 /* router: expert ids and weights [n_rows, top]; rows sorted by expert: group_off (2 * (experts + 1) ints: the offsets,
  * then scratch), sorted_row [n_rows * top] and the position of (row, j) in that order, inv [n_rows * top] */
