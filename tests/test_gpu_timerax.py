@@ -322,7 +322,7 @@ def test_one_far_key_among_hundreds(tmp_path, decoded):
 
 
 # ---- other sizes: values that are often equal, or 1 ------------------------------------------------------------------
-@pytest.mark.parametrize("case", ["single_heads", "wide_heads", "everything_one", "no_rotation_all_keys"])
+@pytest.mark.parametrize("case", ["single_heads", "wide_heads", "everything_one", "no_rotation_all_keys", "odd_sizes"])
 def test_other_sizes(tmp_path, case):
     if case == "single_heads":
         layers = [parallel_cfg(moe_cfg(experts=2, top=1, ff=8, shared=8), heads=1, kv_heads=1, dim=8, vdim=40, chunk=5, rot_dims=8, mheads=1, mdim=40, mvdim=8),
@@ -332,6 +332,10 @@ def test_other_sizes(tmp_path, case):
         layers = [delta_cfg(None, heads=8, kv_heads=1, dim=72, vdim=136, conv=4, rank=16),
                   parallel_cfg(moe_cfg(experts=33, top=5, ff=72, shared=136), heads=8, kv_heads=1, dim=136, vdim=72, chunk=64, rot_dims=70, mheads=1, mdim=136, mvdim=72)]
         width = 200
+    elif case == "odd_sizes":     # nothing a multiple of 4 or 8: every vector path falls back to its scalar form
+        layers = [parallel_cfg(moe_cfg(experts=7, top=3, ff=13, shared=21), heads=3, kv_heads=1, dim=10, vdim=7, chunk=7, rot_dims=6, mheads=2, mdim=7, mvdim=11),
+                  delta_cfg(moe_cfg(experts=3, top=2, ff=9, shared=0), heads=3, kv_heads=1, dim=11, vdim=5, conv=2, rank=3)]
+        width = 53
     elif case == "everything_one":
         layers = [parallel_cfg(moe_cfg(experts=1, top=1, ff=1, shared=1), heads=1, kv_heads=1, dim=2, vdim=1, chunk=1, rot_dims=2, mheads=1, mdim=1, mvdim=1),
                   delta_cfg(None, heads=1, kv_heads=1, dim=1, vdim=1, conv=1, rank=1)]
