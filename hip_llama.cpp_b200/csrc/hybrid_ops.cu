@@ -489,6 +489,210 @@ __global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t 
   }
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// the same attention on the tensor cores, for the bf16 number format and heads of up to 128 channels (multiples of 16 /
+// 8): a block takes 64 (position, query head) pairs of one K/V head, each of its 4 warps 16 of them.  Per tile of 32 keys
+// (aligned to absolute multiples of 32 as above): K rows and TRANSPOSED V rows go to shared memory as bf16; a warp
+// computes its 16 x 32 scores with mma.sync m16n8k16 (q as the A operand from registers), scales and masks them in fp32,
+// keeps the online softmax of its rows among the four lanes that share a row, rounds the weights to bf16 (the row sums
+// add the rounded weights, so that they still sum to one) and multiplies them with V straight from the score registers:
+// two adjacent 8-key score tiles are one 16-deep A operand.  No exchange between warps; accumulators fp32.
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int AM_PAIRS = 64, AM_MAXD = 128;
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(128) hyb_attn_mma_kernel(tha_attn_t a, tha_rows_t rows, tha_kv_t kv, const float* __restrict__ q,
+                                                           __nv_bfloat16* __restrict__ out, int AG, int AP, int splits,
+                                                           float* __restrict__ partial) {
+  extern __shared__ __align__(16) unsigned char smraw[];
+  const int D = a.dim, E = a.vdim, gsize = a.heads / a.kv_heads;
+  const int KS = D + 8, VS = ATT_KEYS + 8;               // padded rows: conflict-free fragment reads
+  __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smraw);   // [32][KS]
+  __nv_bfloat16* Vt = Ks + ATT_KEYS * KS;                        // [E][VS]
+  int seq = -1, r0 = 0, r_end = 0;
+  {
+    int tile = blockIdx.x / splits;
+    for (int s = 0; s < rows.n_seqs; s++) {
+      const int lo = rows.seq_first[s], hi = rows.seq_first[s + 1];
+      const int nt = (hi - lo + AP - 1) / AP;
+      if (tile < nt) { seq = s; r0 = lo + tile * AP; r_end = min(hi, r0 + AP); break; }
+      tile -= nt;
+    }
+    if (seq < 0) return;
+  }
+  const int g = blockIdx.y, part = blockIdx.z;
+  const int slot = rows.seq_slot[seq];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int p_first = rows.pos[r0], p_last = p_first + (r_end - r0) - 1;
+  const int lr = lane >> 2, lc = (lane & 3) * 2;
+  // this lane's two rows (pairs): A = 16 * warp + lr, B = A + 8
+  int row_r[2], row_h[2], row_pos[2], row_first[2];
+  bool row_ok[2];
+#pragma unroll
+  for (int x = 0; x < 2; x++) {
+    const int pr = warp * 16 + lr + 8 * x;
+    const int pp = pr / AG, hg = part * AG + pr % AG;
+    row_r[x] = r0 + pp;
+    row_h[x] = g * gsize + hg;
+    row_ok[x] = pp < AP && row_r[x] < r_end && hg < gsize;
+    row_pos[x] = p_first + pp;
+    row_first[x] = a.chunk > 0 ? (row_pos[x] / a.chunk) * a.chunk : 0;
+  }
+  // q fragments: [k step][4]
+  uint32_t qf[AM_MAXD / 16][4];
+#pragma unroll
+  for (int ks = 0; ks < AM_MAXD / 16; ks++) {
+#pragma unroll
+    for (int x = 0; x < 2; x++) {
+      const float* qr = q + (size_t)row_r[x] * a.heads * D + (size_t)row_h[x] * D;
+      const bool ok = row_ok[x] && 16 * ks < D;
+      qf[ks][x] = ok ? pack_bf16(qr[16 * ks + lc], qr[16 * ks + lc + 1]) : 0u;
+      qf[ks][2 + x] = ok ? pack_bf16(qr[16 * ks + 8 + lc], qr[16 * ks + 8 + lc + 1]) : 0u;
+    }
+  }
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  float oacc[AM_MAXD / 8][4];
+#pragma unroll
+  for (int n = 0; n < AM_MAXD / 8; n++)
+#pragma unroll
+    for (int v = 0; v < 4; v++) oacc[n][v] = 0.f;
+  const int key_lo = a.chunk > 0 ? (p_first / a.chunk) * a.chunk : 0;
+  int kt_begin = (key_lo / ATT_KEYS) * ATT_KEYS, kt_last = p_last;
+  if (splits > 1) {
+    const int n_kt = (p_last - kt_begin) / ATT_KEYS + 1, per = (n_kt + splits - 1) / splits, sp = blockIdx.x % splits;
+    kt_last = min(p_last, kt_begin + (sp + 1) * per * ATT_KEYS - 1);
+    kt_begin += sp * per * ATT_KEYS;
+  }
+  for (int kt = kt_begin; kt <= kt_last; kt += ATT_KEYS) {
+    __syncthreads();
+    // stage the tile: a warp takes 8 keys, four at a time through registers
+    size_t krow[ATT_KEYS / 4];
+#pragma unroll
+    for (int jj = 0; jj < ATT_KEYS / 4; jj++) {
+      const int t = kt + warp + 4 * jj;
+      krow[jj] = (t <= p_last && t >= key_lo) ? hyb_kv_row(kv, slot, t, a.cache_layer) : (size_t)-1;
+    }
+#pragma unroll
+    for (int which = 0; which < 2; which++) {
+      const float* pool = which ? kv.v_pool : kv.k_pool;
+      const int width = which ? E : D;
+#pragma unroll
+      for (int j0 = 0; j0 < ATT_KEYS / 4; j0 += 4) {
+        float buf[4][AM_MAXD / 32];
+#pragma unroll
+        for (int jj = 0; jj < 4; jj++) {
+          const bool live = krow[j0 + jj] != (size_t)-1;
+          const float* src = pool + (live ? krow[j0 + jj] : 0) + (size_t)g * width;
+#pragma unroll
+          for (int c = 0; c < AM_MAXD / 32; c++) buf[jj][c] = (live && lane + 32 * c < width) ? __ldg(src + lane + 32 * c) : 0.f;
+        }
+#pragma unroll
+        for (int jj = 0; jj < 4; jj++) {
+          const int j = warp + 4 * (j0 + jj);
+#pragma unroll
+          for (int c = 0; c < AM_MAXD / 32; c++) {
+            const int d = lane + 32 * c;
+            if (d < width) {
+              if (which) Vt[d * VS + j] = __float2bfloat16_rn(buf[jj][c]);
+              else Ks[j * KS + d] = __float2bfloat16_rn(buf[jj][c]);
+            }
+          }
+        }
+      }
+    }
+    __syncthreads();
+    // scores of this warp's 16 pairs against the 32 keys
+    float sacc[4][4];
+#pragma unroll
+    for (int j = 0; j < 4; j++)
+#pragma unroll
+      for (int v = 0; v < 4; v++) sacc[j][v] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < AM_MAXD / 16; ks++) {
+      if (16 * ks < D) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          uint32_t b[2];
+          const __nv_bfloat16* kr = Ks + (8 * j + lr) * KS + 16 * ks + lc;
+          b[0] = *reinterpret_cast<const uint32_t*>(kr);
+          b[1] = *reinterpret_cast<const uint32_t*>(kr + 8);
+          mma_bf16_16816(sacc[j], qf[ks], b);
+        }
+      }
+    }
+    // scale, mask, online softmax of rows A (values 0, 1 of every score tile) and B (values 2, 3)
+    uint32_t pa[2][4];
+#pragma unroll
+    for (int x = 0; x < 2; x++) {
+      float mx = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 4; j++)
+#pragma unroll
+        for (int y = 0; y < 2; y++) {
+          const int t = kt + 8 * j + lc + y;
+          const bool vis = row_ok[x] && t <= row_pos[x] && t >= row_first[x];
+          const float sv = vis ? sacc[j][2 * x + y] * a.scale : -INFINITY;
+          sacc[j][2 * x + y] = sv;
+          mx = fmaxf(mx, sv);
+        }
+      mx = fmaxf(mx, __shfl_xor_sync(THA_FULL_MASK, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(THA_FULL_MASK, mx, 2));
+      const float m_new = fmaxf(m_run[x], mx);
+      const float corr = m_new > -INFINITY ? expf(m_run[x] - m_new) : 1.f;
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        float p0 = 0.f, p1 = 0.f;
+        if (m_new > -INFINITY) { p0 = expf(sacc[j][2 * x] - m_new); p1 = expf(sacc[j][2 * x + 1] - m_new); }   // exp(-inf) = 0 for masked keys
+        const __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
+        sum += __low2float(pr) + __high2float(pr);
+        pa[j >> 1][(j & 1) * 2 + x] = *reinterpret_cast<const uint32_t*>(&pr);
+      }
+      sum += __shfl_xor_sync(THA_FULL_MASK, sum, 1);
+      sum += __shfl_xor_sync(THA_FULL_MASK, sum, 2);
+      l_run[x] = l_run[x] * corr + sum;
+      m_run[x] = m_new;
+#pragma unroll
+      for (int n = 0; n < AM_MAXD / 8; n++) { oacc[n][2 * x] *= corr; oacc[n][2 * x + 1] *= corr; }
+    }
+    // weights times values: two k steps of 16 keys
+#pragma unroll
+    for (int n = 0; n < AM_MAXD / 8; n++) {
+      if (8 * n < E) {
+#pragma unroll
+        for (int t2 = 0; t2 < 2; t2++) {
+          uint32_t b[2];
+          const __nv_bfloat16* vr = Vt + (8 * n + lr) * VS + 16 * t2 + lc;
+          b[0] = *reinterpret_cast<const uint32_t*>(vr);
+          b[1] = *reinterpret_cast<const uint32_t*>(vr + 8);
+          mma_bf16_16816(oacc[n], pa[t2], b);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int x = 0; x < 2; x++) {
+    if (!row_ok[x]) continue;
+    if (splits > 1) {
+      float* dst = partial + (((size_t)(blockIdx.x % splits) * rows.n_rows + row_r[x]) * a.heads + row_h[x]) * (E + 2);
+#pragma unroll
+      for (int n = 0; n < AM_MAXD / 8; n++)
+        if (8 * n < E) { dst[8 * n + lc] = oacc[n][2 * x]; dst[8 * n + lc + 1] = oacc[n][2 * x + 1]; }
+      if ((lane & 3) == 0) { dst[E] = m_run[x]; dst[E + 1] = l_run[x]; }
+      continue;
+    }
+    const float inv = 1.0f / l_run[x];
+    __nv_bfloat16* dst = out + (size_t)row_r[x] * a.heads * E + (size_t)row_h[x] * E;
+#pragma unroll
+    for (int n = 0; n < AM_MAXD / 8; n++)
+      if (8 * n < E) *reinterpret_cast<__nv_bfloat162*>(dst + 8 * n + lc) = __floats2bfloat162_rn(oacc[n][2 * x] * inv, oacc[n][2 * x + 1] * inv);
+  }
+}
+
 // the splits of a (row, head) in ascending key order: out = sum_s acc_s e^(m_s - M) / sum_s l_s e^(m_s - M); a warp each
 template <typename T>
 __global__ void hyb_attn_merge_kernel(T* __restrict__ out, const float* __restrict__ partial, int n_rows, int heads, int E, int splits) {
@@ -1092,8 +1296,13 @@ extern "C" int tha_hyb_attn(void* stream, int dtype, const tha_attn_t* a, const 
   if (rows->n_rows < 1) return THA_STATUS_SUCCESS;
   if (a->heads % a->kv_heads || a->vdim > 32 * ATT_MAX_VC) return THA_STATUS_NOT_SUPPORTED;
   const int gsize = a->heads / a->kv_heads;
-  const int AG = gsize < ATT_PAIRS ? gsize : ATT_PAIRS, AP = ATT_PAIRS / AG;
-  const size_t smem = sizeof(float) * ((size_t)ATT_PAIRS * a->dim + (size_t)ATT_KEYS * (a->dim + 4) + (size_t)ATT_KEYS * a->vdim + ATT_PAIRS * ATT_KEYS);
+  // bf16 with heads the tensor-core form covers: 64 pairs per block; else 16 pairs on the fp32 cores
+  const bool tc = dtype == THA_DT_BF16 && hyb_tc_linear() && a->dim % 16 == 0 && a->vdim % 8 == 0 && a->dim <= AM_MAXD && a->vdim <= AM_MAXD &&
+                  (a->heads * a->vdim) % 2 == 0;
+  const int pairs = tc ? AM_PAIRS : ATT_PAIRS;
+  const int AG = gsize < pairs ? gsize : pairs, AP = pairs / AG;
+  const size_t smem = tc ? sizeof(__nv_bfloat16) * ((size_t)ATT_KEYS * (a->dim + 8) + (size_t)a->vdim * (ATT_KEYS + 8))
+                         : sizeof(float) * ((size_t)ATT_PAIRS * a->dim + (size_t)ATT_KEYS * (a->dim + 4) + (size_t)ATT_KEYS * a->vdim + ATT_PAIRS * ATT_KEYS);
   if (smem > 227 * 1024) return THA_STATUS_NOT_SUPPORTED;
   // position tiles: at most one ragged tile per sequence beyond rows / AP
   const int tiles = rows->n_rows / AP + rows->n_seqs;
@@ -1110,8 +1319,12 @@ extern "C" int tha_hyb_attn(void* stream, int dtype, const tha_attn_t* a, const 
   const dim3 grid(tiles * splits, a->kv_heads, ceil_div(gsize, AG));
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == THA_DT_BF16) {
-    if (smem > 48 * 1024) THA_CUDA_OK(cudaFuncSetAttribute(hyb_attn_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    THA_CUDA_OK(launch(hyb_attn_kernel<bf16>, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, (bf16*)out, AG, AP, splits, split_scratch));
+    if (tc) {
+      THA_CUDA_OK(launch(hyb_attn_mma_kernel, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, (bf16*)out, AG, AP, splits, split_scratch));
+    } else {
+      if (smem > 48 * 1024) THA_CUDA_OK(cudaFuncSetAttribute(hyb_attn_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      THA_CUDA_OK(launch(hyb_attn_kernel<bf16>, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, (bf16*)out, AG, AP, splits, split_scratch));
+    }
     if (splits > 1)
       THA_CUDA_OK(launch(hyb_attn_merge_kernel<bf16>, dim3(ceil_div(rows->n_rows * a->heads, 4)), dim3(128), 0, s, false, (bf16*)out,
                          (const float*)split_scratch, rows->n_rows, a->heads, a->vdim, splits));

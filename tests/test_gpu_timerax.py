@@ -437,3 +437,30 @@ def test_prompt_sized_step_runs_the_experts_one_matmul_each(tmp_path, monkeypatc
     got2 = feed(small, "a", toks, [500])[::7]
     assert rel_err(got2, z[::7]) < BF16_TOL
     assert rel_err(got2, got) < BF16_TOL / 2
+
+
+@pytest.mark.parametrize("chunk,cuts", [(48, [150]), (48, [47, 2, 1]), (512, [380, 1]), (512, [33, 200, 1])])
+def test_tensor_core_attention_bfloat16(tmp_path, chunk, cuts):
+    """bfloat16 with heads of 64 / 32 channels takes the tensor-core form of the attention (64 pairs per block, weights
+    and values in bf16).  Peaked scores (a few keys carry a query's weight) and a check of EVERY position by itself: the
+    first positions of a block of positions see one, two, three keys, so a key too many or too few there is an error of
+    tens of percent, and a skipped tile of keys shows at the positions whose heavy keys lie in it."""
+    cfg = model_cfg([parallel_cfg(None, heads=4, kv_heads=2, dim=64, vdim=32, chunk=chunk, rot_dims=32, scale=0.5)], width=64, vocab=200,
+                    softcap=0)
+    b = Built(tmp_path, cfg, 41, _zero(["l0.mix.right.out"]))
+    n = 150 if chunk == 48 else 400
+    toks = tokens_for(b, n, chunk)
+    _, layers = b.ref(toks)
+    mix = layers[0] - b.w["embed"][toks]                 # the attention side alone (normed, halved)
+    e = b.engine("bfloat16")
+    at, got = 0, []
+    for c in cuts + [cuts[-1]] * n:
+        c = min(c, n - at)
+        if c <= 0:
+            break
+        got.append(e.step([("a", toks[at:at + c], [])], taps=True)[1][0])
+        at += c
+    got = np.concatenate(got, 0) - b.w["embed"][toks]
+    worst = max(rel_err(got[p], mix[p]) for p in range(n))
+    assert worst < 6e-2, worst
+    assert rel_err(got, mix) < 2e-2
