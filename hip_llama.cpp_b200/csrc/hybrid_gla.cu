@@ -1,0 +1,110 @@
+// Gated linear attention (tha_gla_t): per head S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t / sqrt(dim).
+//   hyb_gla_decay_kernel   all rows at once, in place: z + b -> a = sigmoid(z + b)^(1/tau) = exp(-softplus(-(z + b)) / tau)
+//   hyb_gla_scan_kernel    the recurrence with the state in registers: a warp owns GLA_COLS value columns of one
+//                          (sequence, head), lane l the key channels l, l + 32, ...; the column sums S^T q are warp
+//                          shuffles, the next token's inputs are fetched while the current one is computed; no barrier.
+//                          The state is read from the sequence's slot before its first row of the step and written back
+//                          after its last, so a prompt cut anywhere continues exactly where it stopped.
+// Decays, state and read-out are fp32 in both number formats; the head norm and the silu gate follow in
+// tha_hyb_head_gate.
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+#include "hybrid_ops.cuh"
+#include "tha_hybrid.h"
+
+namespace tha {
+
+constexpr int GLA_COLS = 2, GLA_WARPS = 4;
+
+__global__ void hyb_gla_decay_kernel(float* __restrict__ z, size_t n, int hd, const float* __restrict__ bias, float inv_tau) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float v = z[i] + (bias ? bias[i % hd] : 0.f);
+  z[i] = expf(-hyb_softplus(-v) * inv_tau);
+}
+
+template <int RPL>
+__global__ void __launch_bounds__(32 * GLA_WARPS) hyb_gla_scan_kernel(tha_gla_t g, tha_rows_t rows, tha_state_store_t st,
+                                                                      const float* __restrict__ proj, long long ldp,
+                                                                      const float* __restrict__ decay, float* __restrict__ o_raw) {
+  const int s = blockIdx.x, h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int D = g.dim, E = g.vdim;
+  const int e0 = (blockIdx.z * GLA_WARPS + warp) * GLA_COLS;
+  if (e0 >= E) return;
+  float* gstate = st.base + (size_t)rows.seq_slot[s] * st.slot_floats + g.state_off + (size_t)h * D * E;
+  float S[RPL][GLA_COLS];
+#pragma unroll
+  for (int i = 0; i < RPL; i++) {
+    const int d = lane + 32 * i;
+#pragma unroll
+    for (int c = 0; c < GLA_COLS; c++) S[i][c] = (d < D && e0 + c < E) ? gstate[(size_t)d * E + e0 + c] : 0.f;
+  }
+  const float qscale = 1.0f / sqrtf((float)D);
+  const int r_begin = rows.seq_first[s], r_end = rows.seq_first[s + 1];
+  float q[RPL], k[RPL], a[RPL], v[GLA_COLS];
+  auto fetch = [&](int r) {
+    const float* x = proj + (size_t)r * ldp;
+#pragma unroll
+    for (int i = 0; i < RPL; i++) {
+      const int d = lane + 32 * i;
+      q[i] = d < D ? x[g.o_q + h * D + d] * qscale : 0.f;
+      k[i] = d < D ? x[g.o_k + h * D + d] : 0.f;
+      a[i] = d < D ? decay[(size_t)r * g.heads * D + h * D + d] : 0.f;
+    }
+#pragma unroll
+    for (int c = 0; c < GLA_COLS; c++) v[c] = e0 + c < E ? x[g.o_v + h * E + e0 + c] : 0.f;
+  };
+  if (r_begin < r_end) fetch(r_begin);
+  for (int r = r_begin; r < r_end; r++) {
+    float o[GLA_COLS];
+#pragma unroll
+    for (int c = 0; c < GLA_COLS; c++) o[c] = 0.f;
+#pragma unroll
+    for (int i = 0; i < RPL; i++)
+#pragma unroll
+      for (int c = 0; c < GLA_COLS; c++) {
+        S[i][c] = fmaf(S[i][c], a[i], k[i] * v[c]);
+        o[c] = fmaf(S[i][c], q[i], o[c]);
+      }
+    if (r + 1 < r_end) fetch(r + 1);
+#pragma unroll
+    for (int c = 0; c < GLA_COLS; c++) {
+      const float ov = warp_sum(o[c]);
+      if (lane == c && e0 + c < E) o_raw[(size_t)r * g.heads * E + (size_t)h * E + e0 + c] = ov;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < RPL; i++) {
+    const int d = lane + 32 * i;
+    if (d >= D) continue;
+#pragma unroll
+    for (int c = 0; c < GLA_COLS; c++)
+      if (e0 + c < E) gstate[(size_t)d * E + e0 + c] = S[i][c];
+  }
+}
+
+}  // namespace tha
+
+using namespace tha;
+
+extern "C" int tha_hyb_gla_scan(void* stream, int dtype, const tha_gla_t* g, const tha_rows_t* rows, const tha_state_store_t* st,
+                                const float* proj, long long ldp, float* z_raw, float* o_raw, void* out) {
+  if (rows->n_seqs < 1 || rows->n_rows < 1) return THA_STATUS_SUCCESS;
+  if (g->heads < 1 || g->dim < 1 || g->vdim < 1 || !(g->tau > 0.f)) return THA_STATUS_INVALID_ARG;
+  if (g->dim > 512) return THA_STATUS_NOT_SUPPORTED;   // 16 key channels per lane is the widest register form
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t n = (size_t)rows->n_rows * g->heads * g->dim;
+  THA_CUDA_OK(launch(hyb_gla_decay_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, false, z_raw, n, g->heads * g->dim, g->b_a2,
+                     1.0f / g->tau));
+  const dim3 grid(rows->n_seqs, g->heads, ceil_div(g->vdim, GLA_COLS * GLA_WARPS)), block(32 * GLA_WARPS);
+  const float* dec = z_raw;
+#define GLA_LAUNCH(R) THA_CUDA_OK(launch(hyb_gla_scan_kernel<R>, grid, block, 0, s, false, *g, *rows, *st, proj, ldp, dec, o_raw))
+  if (g->dim <= 32) GLA_LAUNCH(1);
+  else if (g->dim <= 64) GLA_LAUNCH(2);
+  else if (g->dim <= 128) GLA_LAUNCH(4);
+  else if (g->dim <= 256) GLA_LAUNCH(8);
+  else GLA_LAUNCH(16);
+#undef GLA_LAUNCH
+  return tha_hyb_head_gate(stream, dtype, out, o_raw, rows->n_rows, g->heads, g->vdim, 1, g->eps, g->norm, 0, proj + g->o_g, ldp, THA_GATE_SILU);
+}

@@ -34,6 +34,15 @@ __global__ void hyb_rmsnorm_kernel(T* __restrict__ out, const float* __restrict_
   for (int i = threadIdx.x; i < width; i += blockDim.x) hyb_store(out + (size_t)r * width + i, xr[i] * inv * (w_offset + (w ? w[i] : 0.f)));
 }
 
+// dynamic tanh: tanh(alpha x) w + b, element by element (no mean, no variance)
+template <typename T>
+__global__ void hyb_dyt_kernel(T* __restrict__ out, const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
+                               float alpha, int width, const int* __restrict__ rows_idx) {
+  const int r = blockIdx.x;
+  const float* xr = x + (size_t)(rows_idx ? rows_idx[r] : r) * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) hyb_store(out + (size_t)r * width + i, fmaf(tanhf(alpha * xr[i]), w[i], b ? b[i] : 0.f));
+}
+
 // ------------------------------------------------------------------------------------------------------------------
 // linear: 64 x 64 output tile per block, 16-deep k slices through shared memory, 4 x 4 per thread, fp32 FMA in
 // ascending k: the sum of an output element is the same whatever tile or group it lands in.
@@ -44,9 +53,12 @@ template <typename TA, typename TW>
 __global__ void __launch_bounds__(256) hyb_linear_kernel(float* __restrict__ C, long long ldc, const TA* __restrict__ A, long long lda,
                                                          const int* __restrict__ a_rows, const TW* __restrict__ W,
                                                          long long w_group_stride, int M, int N, int K,
-                                                         const int* __restrict__ group_off, int n_groups) {
+                                                         const int* __restrict__ group_off, int n_groups, long long a_zs, long long w_zs,
+                                                         long long c_zs) {
   __shared__ float As[LK][LT + 4];
   __shared__ float Ws[LK][LT + 4];
+  // blockIdx.z: one independent product per head (strides in elements), 0 strides otherwise
+  A += (size_t)blockIdx.z * a_zs; W += (size_t)blockIdx.z * w_zs; C += (size_t)blockIdx.z * c_zs;
   // which group and which rows this block covers
   int g = 0, m0 = 0, m_end = M;
   if (group_off) {
@@ -121,9 +133,11 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a
 __global__ void __launch_bounds__(128) hyb_linear_mma_kernel(float* __restrict__ C, long long ldc, const __nv_bfloat16* __restrict__ A,
                                                              long long lda, const int* __restrict__ a_rows,
                                                              const __nv_bfloat16* __restrict__ W, long long w_group_stride, int M, int N,
-                                                             int K, const int* __restrict__ group_off, int n_groups) {
+                                                             int K, const int* __restrict__ group_off, int n_groups, long long a_zs,
+                                                             long long w_zs, long long c_zs) {
   __shared__ __align__(16) __nv_bfloat16 As[LT][MKP];
   __shared__ __align__(16) __nv_bfloat16 Ws[LT][MKP];
+  A += (size_t)blockIdx.z * a_zs; W += (size_t)blockIdx.z * w_zs; C += (size_t)blockIdx.z * c_zs;
   int g = 0, m0 = 0, m_end = M;
   if (group_off) {
     int tile = blockIdx.y, found = 0;
@@ -227,10 +241,6 @@ __global__ void hyb_rotary_kernel(const double* __restrict__ inv_freq, int half,
 // ------------------------------------------------------------------------------------------------------------------
 // attention preparation: one block per row, one warp per head (query heads first, then key heads, then value heads)
 // ------------------------------------------------------------------------------------------------------------------
-__device__ __forceinline__ size_t hyb_kv_row(const tha_kv_t& kv, int slot, int t, int layer) {
-  const int blk = kv.table[(size_t)slot * kv.table_stride + t / kv.block_size];
-  return ((size_t)blk * kv.n_cache_layers + layer) * kv.block_size * kv.kv_dim + (size_t)(t % kv.block_size) * kv.kv_dim;
-}
 
 __global__ void hyb_attn_prepare_kernel(tha_attn_t a, tha_rows_t rows, tha_kv_t kv, const float* __restrict__ proj, long long ldp,
                                         const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot_dims,
@@ -715,10 +725,6 @@ __global__ void hyb_attn_merge_kernel(T* __restrict__ out, const float* __restri
 // matrix memory: one block per (sequence, head); S [dim, vdim], n [dim] in shared memory, tokens in order.
 // ------------------------------------------------------------------------------------------------------------------
 
-__device__ __forceinline__ float hyb_softcap(float z, float cap) { return cap * tanhf(z / cap); }
-__device__ __forceinline__ float hyb_logsigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
-__device__ __forceinline__ float hyb_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
-__device__ __forceinline__ float hyb_softplus(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
 
 // The scalar arithmetic of the gates does not depend on the state, so it runs for all rows at once before the scans and
 // in place: the two gate columns of the stacked projection become the log input gate cap * tanh((z + b) / cap) and the log
@@ -1015,18 +1021,25 @@ __global__ void __launch_bounds__(32 * SCAN_WARPS) hyb_delta_scan_warp_kernel(th
 // out = o / rms(o over the head) * norm * sigmoid(gate), dtype-typed; a warp per (row, head)
 template <typename T>
 __global__ void hyb_head_gate_kernel(T* __restrict__ out, const float* __restrict__ o_raw, int n_rows, int heads, int E, float eps,
-                                     const float* __restrict__ norm, int norm_per_head, const float* __restrict__ gate, long long ldg) {
+                                     const float* __restrict__ norm, int norm_per_head, const float* __restrict__ gate, long long ldg,
+                                     int do_norm, int gate_act) {
   const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (idx >= n_rows * heads) return;
   const int r = idx / heads, h = idx - r * heads;
   const float* o = o_raw + (size_t)r * heads * E + (size_t)h * E;
-  float ss = 0.f;
-  for (int e = lane; e < E; e += 32) ss = fmaf(o[e], o[e], ss);
-  ss = warp_sum(ss);
-  const float inv = 1.0f / sqrtf(ss / (float)E + eps);
-  for (int e = lane; e < E; e += 32)
-    hyb_store(out + (size_t)r * heads * E + (size_t)h * E + e,
-              o[e] * inv * norm[norm_per_head ? h * E + e : e] * hyb_sigmoid(gate[(size_t)r * ldg + h * E + e]));
+  float inv = 1.0f;
+  if (do_norm) {
+    float ss = 0.f;
+    for (int e = lane; e < E; e += 32) ss = fmaf(o[e], o[e], ss);
+    ss = warp_sum(ss);
+    inv = 1.0f / sqrtf(ss / (float)E + eps);
+  }
+  for (int e = lane; e < E; e += 32) {
+    const float z = gate[(size_t)r * ldg + h * E + e];
+    const float g = gate_act == THA_GATE_SILU ? z * hyb_sigmoid(z) : hyb_sigmoid(z);
+    const float v = do_norm ? o[e] * inv * norm[norm_per_head ? h * E + e : e] : o[e];
+    hyb_store(out + (size_t)r * heads * E + (size_t)h * E + e, v * g);
+  }
 }
 
 // ------------------------------------------------------------------------------------------------------------------
@@ -1173,6 +1186,89 @@ __global__ void hyb_route_kernel(int experts, int top, int o_router, const float
   }
   if (lane < top) weight[(size_t)r * top + lane] = expf(mine - zmax) / sum;
 }
+// Router with scores over ALL experts: s = softmax(z); the choice uses s + correction, limited to the `keep` groups (of
+// experts / groups neighbours each) whose largest choice score is highest -- experts outside them count as minus infinity,
+// whatever the sign of their score; the weights are the chosen s over their sum.  A warp per row; ties go to the lowest
+// index; needs top <= 32 and groups <= 32 (lane g keeps group g's best).
+__global__ void hyb_route_groups_kernel(int experts, int top, int groups, int keep, int o_router, const float* __restrict__ correction,
+                                        const float* __restrict__ proj, long long ldp, int n_rows, int* __restrict__ expert_id,
+                                        float* __restrict__ weight, int* __restrict__ counts) {
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (r >= n_rows) return;
+  const float* z = proj + (size_t)r * ldp + o_router;
+  float zmax = -INFINITY;
+  for (int e = lane; e < experts; e += 32) zmax = fmaxf(zmax, z[e]);
+  for (int o = 16; o > 0; o >>= 1) zmax = fmaxf(zmax, __shfl_xor_sync(THA_FULL_MASK, zmax, o));
+  float den = 0.f;
+  for (int e = lane; e < experts; e += 32) den += expf(z[e] - zmax);
+  den = warp_sum(den);
+  unsigned allowed = 0xffffffffu;   // bit g: group g may be chosen from
+  const int per = groups > 1 ? experts / groups : experts;
+  if (groups > 1 && keep < groups) {
+    float gbest = -INFINITY;         // lane g: the largest choice score of group g
+    if (lane < groups)
+      for (int e = lane * per; e < (lane + 1) * per; e++) gbest = fmaxf(gbest, expf(z[e] - zmax) / den + (correction ? correction[e] : 0.f));
+    allowed = 0u;
+    for (int j = 0; j < keep; j++) {
+      float best = (lane < groups && !((allowed >> lane) & 1u)) ? gbest : -INFINITY;
+      int bi = (lane < groups && !((allowed >> lane) & 1u)) ? lane : 0x7fffffff;
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(THA_FULL_MASK, best, o);
+        const int oi = __shfl_xor_sync(THA_FULL_MASK, bi, o);
+        if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+      }
+      if (bi < groups) allowed |= 1u << bi;
+    }
+  }
+  float sum = 0.f, mine = 0.f;
+  unsigned long long taken_lo = 0ull;   // experts this lane has given away (bit = e / 32 of its own stride), up to 2048 experts
+  unsigned long long taken_hi = 0ull;
+  for (int j = 0; j < top; j++) {
+    float best = -INFINITY, bs = 0.f; int bi = 0x7fffffff;
+    for (int e = lane, n = 0; e < experts; e += 32, n++) {
+      const bool taken = n < 64 ? (taken_lo >> n) & 1ull : (taken_hi >> (n - 64)) & 1ull;
+      if (taken || !((allowed >> (groups > 1 ? e / per : 0)) & 1u)) continue;
+      const float sc = expf(z[e] - zmax) / den;
+      const float v = sc + (correction ? correction[e] : 0.f);
+      if (v > best || (v == best && e < bi)) { best = v; bi = e; bs = sc; }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(THA_FULL_MASK, best, o);
+      const int oi = __shfl_xor_sync(THA_FULL_MASK, bi, o);
+      const float os = __shfl_xor_sync(THA_FULL_MASK, bs, o);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; bs = os; }
+    }
+    if (bi >= experts) bi = 0, bs = 0.f;   // fewer allowed experts than picks: cannot happen with a valid config
+    if ((bi & 31) == lane) { const int n = bi >> 5; if (n < 64) taken_lo |= 1ull << n; else taken_hi |= 1ull << (n - 64); }
+    if (lane == 0) { expert_id[(size_t)r * top + j] = bi; atomicAdd(counts + bi, 1); }
+    if (lane == j) mine = bs;
+    sum += bs;
+  }
+  if (lane < top) weight[(size_t)r * top + lane] = mine / (sum + 1e-20f);
+}
+
+// any of the feed-forward activations (THA_ACT_*): gated ones read columns col_g and col_u, ungated ones col_u only
+template <typename T>
+__global__ void hyb_ff_act_kernel(T* __restrict__ y, const float* __restrict__ gu, long long ldg, int col_g, int col_u, int n, int ff, int act,
+                                  float limit, float alpha) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)n * ff) return;
+  const size_t r = i / ff; const int c = (int)(i - r * ff);
+  const float u = gu[r * ldg + col_u + c];
+  float v;
+  if (act == THA_ACT_RELU2) {
+    const float p = fmaxf(u, 0.f);
+    v = p * p;
+  } else if (act == THA_ACT_GELU_TANH_GLU) {
+    const float g = gu[r * ldg + col_g + c];
+    v = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+  } else {
+    const float g = fminf(gu[r * ldg + col_g + c], limit);
+    v = g * hyb_sigmoid(alpha * g) * (fminf(fmaxf(u, -limit), limit) + 1.0f);
+  }
+  hyb_store(y + i, v);
+}
+
 // counting sort of the (row, pick) pairs by expert, one block, a warp per expert: within an expert the pairs stay in
 // ascending (row, pick) order, so the placement is the same on every run.
 __global__ void hyb_route_sort_kernel(int experts, int top, int n_rows, const int* __restrict__ expert_id, const int* __restrict__ counts,
@@ -1196,17 +1292,6 @@ __global__ void hyb_route_sort_kernel(int experts, int top, int n_rows, const in
       at += __popc(m);
     }
   }
-}
-
-template <typename T>
-__global__ void hyb_glu_kernel(T* __restrict__ y, const float* __restrict__ gu, long long ldg, int col_g, int col_u, int n, int ff,
-                               float limit, float alpha) {
-  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= (size_t)n * ff) return;
-  const size_t r = i / ff; const int c = (int)(i - r * ff);
-  const float g = fminf(gu[r * ldg + col_g + c], limit);
-  const float u = fminf(fmaxf(gu[r * ldg + col_u + c], -limit), limit);
-  hyb_store(y + i, g * hyb_sigmoid(alpha * g) * (u + 1.0f));
 }
 
 // THA_HYB_TC=0 keeps every product on the plain kernel (A/B aid)
@@ -1238,6 +1323,57 @@ extern "C" int tha_hyb_rmsnorm(void* stream, int dtype, void* out, const float* 
   return THA_STATUS_SUCCESS;
 }
 
+extern "C" int tha_hyb_norm(void* stream, int dtype, void* out, const float* x, const tha_norm_t* n, float eps, int n_rows, int width,
+                            const int* rows_idx) {
+  if (n->kind == THA_NORM_RMS) return tha_hyb_rmsnorm(stream, dtype, out, x, n->w, n->w_offset, eps, n_rows, width, rows_idx);
+  if (n->kind != THA_NORM_DYT || !n->w) return THA_STATUS_INVALID_ARG;
+  if (n_rows < 1) return THA_STATUS_SUCCESS;
+  const int nt = pick_threads(width);
+  if (dtype == THA_DT_BF16)
+    THA_CUDA_OK(launch(hyb_dyt_kernel<bf16>, dim3(n_rows), dim3(nt), 0, (cudaStream_t)stream, false, (bf16*)out, x, n->w, n->b, n->alpha, width, rows_idx));
+  else
+    THA_CUDA_OK(launch(hyb_dyt_kernel<float>, dim3(n_rows), dim3(nt), 0, (cudaStream_t)stream, false, (float*)out, x, n->w, n->b, n->alpha, width, rows_idx));
+  return THA_STATUS_SUCCESS;
+}
+
+extern "C" int tha_hyb_linear_heads(void* stream, int dtype, float* C, long long ldc, long long c_hs, const void* A, long long lda,
+                                    long long a_hs, int a_f32, const void* W, long long w_hs, int M, int N, int K, int heads) {
+  if (M < 1 || N < 1 || heads < 1) return THA_STATUS_SUCCESS;
+  if (K < 1 || !C || !A || !W) return THA_STATUS_INVALID_ARG;
+  cudaStream_t s = (cudaStream_t)stream;
+  const dim3 grid(ceil_div(N, LT), ceil_div(M, LT), heads), block(256);
+  const int* none = nullptr;
+  if (dtype == THA_DT_BF16 && !a_f32 && hyb_tc_linear() && K % 8 == 0 && lda % 8 == 0 && a_hs % 8 == 0 && w_hs % 8 == 0 && aligned16(A) && aligned16(W)) {
+    THA_CUDA_OK(launch(hyb_linear_mma_kernel, grid, dim3(128), 0, s, false, C, ldc, (const bf16*)A, lda, none, (const bf16*)W, 0ll, M, N, K, none, 0,
+                       a_hs, w_hs, c_hs));
+    return THA_STATUS_SUCCESS;
+  }
+  if (dtype == THA_DT_F32)
+    THA_CUDA_OK(launch(hyb_linear_kernel<float, float>, grid, block, 0, s, false, C, ldc, (const float*)A, lda, none, (const float*)W, 0ll, M, N, K,
+                       none, 0, a_hs, w_hs, c_hs));
+  else if (a_f32)
+    THA_CUDA_OK(launch(hyb_linear_kernel<float, bf16>, grid, block, 0, s, false, C, ldc, (const float*)A, lda, none, (const bf16*)W, 0ll, M, N, K,
+                       none, 0, a_hs, w_hs, c_hs));
+  else
+    THA_CUDA_OK(launch(hyb_linear_kernel<bf16, bf16>, grid, block, 0, s, false, C, ldc, (const bf16*)A, lda, none, (const bf16*)W, 0ll, M, N, K,
+                       none, 0, a_hs, w_hs, c_hs));
+  return THA_STATUS_SUCCESS;
+}
+
+extern "C" int tha_hyb_head_gate(void* stream, int dtype, void* out, const float* o_raw, int n_rows, int heads, int E, int do_norm,
+                                 float eps, const float* norm, int norm_per_head, const float* gate, long long ldg, int gate_act) {
+  if (n_rows < 1) return THA_STATUS_SUCCESS;
+  if (!gate || (do_norm && !norm)) return THA_STATUS_INVALID_ARG;
+  const dim3 grid(ceil_div(n_rows * heads, 4));
+  if (dtype == THA_DT_BF16)
+    THA_CUDA_OK(launch(hyb_head_gate_kernel<bf16>, grid, dim3(128), 0, (cudaStream_t)stream, false, (bf16*)out, o_raw, n_rows, heads, E, eps, norm,
+                       norm_per_head, gate, ldg, do_norm, gate_act));
+  else
+    THA_CUDA_OK(launch(hyb_head_gate_kernel<float>, grid, dim3(128), 0, (cudaStream_t)stream, false, (float*)out, o_raw, n_rows, heads, E, eps, norm,
+                       norm_per_head, gate, ldg, do_norm, gate_act));
+  return THA_STATUS_SUCCESS;
+}
+
 extern "C" int tha_hyb_linear(void* stream, int dtype, float* C, long long ldc, const void* A, long long lda, int a_f32,
                               const int* a_rows, const void* W, long long w_group_stride, int M, int N, int K,
                               const int* group_off, int n_groups) {
@@ -1257,18 +1393,18 @@ extern "C" int tha_hyb_linear(void* stream, int dtype, float* C, long long ldc, 
   const dim3 grid(ceil_div(N, LT), mt), block(256);
   if (dtype == THA_DT_BF16 && !a_f32 && hyb_tc_linear() && K % 8 == 0 && lda % 8 == 0 && w_group_stride % 8 == 0 && aligned16(A) && aligned16(W)) {
     THA_CUDA_OK(launch(hyb_linear_mma_kernel, grid, dim3(128), 0, s, false, C, ldc, (const bf16*)A, lda, a_rows, (const bf16*)W, w_group_stride,
-                       M, N, K, group_off, n_groups));
+                       M, N, K, group_off, n_groups, 0ll, 0ll, 0ll));
     return THA_STATUS_SUCCESS;
   }
   if (dtype == THA_DT_F32)
     THA_CUDA_OK(launch(hyb_linear_kernel<float, float>, grid, block, 0, s, false, C, ldc, (const float*)A, lda, a_rows, (const float*)W,
-                       w_group_stride, M, N, K, group_off, n_groups));
+                       w_group_stride, M, N, K, group_off, n_groups, 0ll, 0ll, 0ll));
   else if (a_f32)
     THA_CUDA_OK(launch(hyb_linear_kernel<float, bf16>, grid, block, 0, s, false, C, ldc, (const float*)A, lda, a_rows, (const bf16*)W,
-                       w_group_stride, M, N, K, group_off, n_groups));
+                       w_group_stride, M, N, K, group_off, n_groups, 0ll, 0ll, 0ll));
   else
     THA_CUDA_OK(launch(hyb_linear_kernel<bf16, bf16>, grid, block, 0, s, false, C, ldc, (const bf16*)A, lda, a_rows, (const bf16*)W,
-                       w_group_stride, M, N, K, group_off, n_groups));
+                       w_group_stride, M, N, K, group_off, n_groups, 0ll, 0ll, 0ll));
   return THA_STATUS_SUCCESS;
 }
 
@@ -1350,7 +1486,7 @@ template <typename T>
 static int head_gate_launch(cudaStream_t s, T* out, const float* o_raw, int n_rows, int heads, int E, float eps, const float* norm,
                             int norm_per_head, const float* gate, long long ldg) {
   THA_CUDA_OK(launch(hyb_head_gate_kernel<T>, dim3(ceil_div(n_rows * heads, 4)), dim3(128), 0, s, false, out, o_raw, n_rows, heads, E, eps, norm,
-                     norm_per_head, gate, ldg));
+                     norm_per_head, gate, ldg, 1, (int)THA_GATE_SIGMOID));
   return THA_STATUS_SUCCESS;
 }
 
@@ -1429,21 +1565,33 @@ extern "C" int tha_hyb_moe_route(void* stream, const tha_moe_t* e, const float* 
   cudaStream_t s = (cudaStream_t)stream;
   int* counts = group_off + e->experts + 1;   // the second half of group_off is the routers' counters
   THA_CUDA_OK(cudaMemsetAsync(counts, 0, sizeof(int) * e->experts, s));
-  THA_CUDA_OK(launch(hyb_route_kernel, dim3(ceil_div(n_rows, 4)), dim3(128), 0, s, false, e->experts, e->top, e->o_router, proj, ldp, n_rows,
-                     expert_id, weight, counts));
+  if (e->route == THA_ROUTE_SOFTMAX_GROUPS) {
+    const int groups = e->groups > 1 ? e->groups : 1;
+    if (groups > 32 || e->experts % groups || e->experts > 4096 || e->keep_groups < 1) return THA_STATUS_INVALID_ARG;
+    THA_CUDA_OK(launch(hyb_route_groups_kernel, dim3(ceil_div(n_rows, 4)), dim3(128), 0, s, false, e->experts, e->top, groups,
+                       e->keep_groups < groups ? e->keep_groups : groups, e->o_router, e->correction, proj, ldp, n_rows, expert_id, weight, counts));
+  } else {
+    THA_CUDA_OK(launch(hyb_route_kernel, dim3(ceil_div(n_rows, 4)), dim3(128), 0, s, false, e->experts, e->top, e->o_router, proj, ldp, n_rows,
+                       expert_id, weight, counts));
+  }
   const int nt = 32 * (e->experts < 32 ? e->experts : 32);
   THA_CUDA_OK(launch(hyb_route_sort_kernel, dim3(1), dim3(nt), sizeof(int) * (e->experts + 1), s, false, e->experts, e->top, n_rows,
                      (const int*)expert_id, (const int*)counts, group_off, sorted_row, inv));
   return THA_STATUS_SUCCESS;
 }
 
-extern "C" int tha_hyb_glu_clamped(void* stream, int dtype, void* y, const float* gu, long long ldg, int col_g, int col_u, int n,
-                                   int ff, float limit, float alpha) {
-  if (n < 1) return THA_STATUS_SUCCESS;
+extern "C" int tha_hyb_ff_act(void* stream, int dtype, int act, void* y, const float* gu, long long ldg, int col_g, int col_u, int n,
+                              int ff, float limit, float alpha) {
+  if (n < 1 || ff < 1) return THA_STATUS_SUCCESS;
   const dim3 grid((unsigned)(((size_t)n * ff + 255) / 256));
   if (dtype == THA_DT_BF16)
-    THA_CUDA_OK(launch(hyb_glu_kernel<bf16>, grid, dim3(256), 0, (cudaStream_t)stream, false, (bf16*)y, gu, ldg, col_g, col_u, n, ff, limit, alpha));
+    THA_CUDA_OK(launch(hyb_ff_act_kernel<bf16>, grid, dim3(256), 0, (cudaStream_t)stream, false, (bf16*)y, gu, ldg, col_g, col_u, n, ff, act, limit, alpha));
   else
-    THA_CUDA_OK(launch(hyb_glu_kernel<float>, grid, dim3(256), 0, (cudaStream_t)stream, false, (float*)y, gu, ldg, col_g, col_u, n, ff, limit, alpha));
+    THA_CUDA_OK(launch(hyb_ff_act_kernel<float>, grid, dim3(256), 0, (cudaStream_t)stream, false, (float*)y, gu, ldg, col_g, col_u, n, ff, act, limit, alpha));
   return THA_STATUS_SUCCESS;
+}
+
+extern "C" int tha_hyb_glu_clamped(void* stream, int dtype, void* y, const float* gu, long long ldg, int col_g, int col_u, int n,
+                                   int ff, float limit, float alpha) {
+  return tha_hyb_ff_act(stream, dtype, THA_ACT_GLU_CLAMPED, y, gu, ldg, col_g, col_u, n, ff, limit, alpha);
 }

@@ -14,20 +14,25 @@
 
 namespace tha {
 
+// x = embed[token] (+ the learned vector of the row's position when the model has a position table)
 template <typename T>
-__global__ void hyb_embed_kernel(float* __restrict__ x, const T* __restrict__ embed, const int* __restrict__ token, int width) {
+__global__ void hyb_embed_kernel(float* __restrict__ x, const T* __restrict__ embed, const int* __restrict__ token, int width,
+                                 const T* __restrict__ pos_embed, const int* __restrict__ pos) {
   const int r = blockIdx.x;
   const T* e = embed + (size_t)token[r] * width;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) x[(size_t)r * width + i] = hyb_load(e + i);
+  const T* p = pos_embed ? pos_embed + (size_t)pos[r] * width : nullptr;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) x[(size_t)r * width + i] = hyb_load(e + i) + (p ? hyb_load(p + i) : 0.f);
 }
 
-// x += mixer + feed-forward.  Two-sided mixers: each side's projection is normed over the width with its own weight,
+// x += scale_mix * mixer + scale_ff * feed-forward (layer scales optional).  Two-sided mixers: each side's projection is normed over the width with its own weight,
 // the mixer is half their sum.  Feed-forward: the chosen experts' outputs by router weight (found through `inv` in the
-// expert-sorted buffer), plus the shared expert.
+// expert-sorted buffer), plus the shared expert (times sigmoid of the row's shared_gate entry when given); a dense
+// feed-forward arrives as `shared_down` alone.
 __global__ void hyb_finish_kernel(float* __restrict__ x, int width, float eps, const float* __restrict__ left, const float* __restrict__ right,
                                   const float* __restrict__ w_left, const float* __restrict__ w_right, int top,
                                   const float* __restrict__ weight, const int* __restrict__ inv, const float* __restrict__ down,
-                                  const float* __restrict__ shared_down, float* __restrict__ tap) {
+                                  const float* __restrict__ shared_down, const float* __restrict__ shared_gate, long long ld_shared_gate,
+                                  const float* __restrict__ scale_mix, const float* __restrict__ scale_ff, float* __restrict__ tap) {
   __shared__ float red[33];
   const int r = blockIdx.x;
   const float* l = left + (size_t)r * width;
@@ -41,11 +46,14 @@ __global__ void hyb_finish_kernel(float* __restrict__ x, int width, float eps, c
     il = 1.0f / sqrtf(sl / (float)width + eps);
     ir = 1.0f / sqrtf(sr / (float)width + eps);
   }
+  const float sg = shared_gate ? 1.0f / (1.0f + expf(-shared_gate[(size_t)r * ld_shared_gate])) : 1.0f;
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     float y = right ? 0.5f * (l[i] * il * w_left[i] + right[(size_t)r * width + i] * ir * w_right[i]) : l[i];
     float f = 0.f;
     for (int j = 0; j < top; j++) f = fmaf(weight[(size_t)r * top + j], down[(size_t)inv[(size_t)r * top + j] * width + i], f);
-    if (shared_down) f += shared_down[(size_t)r * width + i];
+    if (shared_down) f = fmaf(shared_down[(size_t)r * width + i], sg, f);
+    if (scale_mix) y *= scale_mix[i];
+    if (scale_ff) f *= scale_ff[i];
     const float v = x[(size_t)r * width + i] + (y + f);
     x[(size_t)r * width + i] = v;
     if (tap) tap[(size_t)r * width + i] = v;
@@ -82,7 +90,8 @@ struct Carver {
 
 struct StepBuffers {
   float *x, *proj, *q, *left, *right, *conv, *dt_raw, *gate_raw, *gu, *down, *sdown, *weight, *oraw, *split; size_t split_floats;
-  void *h, *abuf, *mbuf, *y, *sy, *hn, *hg;
+  float *proj2, *qfull;
+  void *h, *h2, *cq, *qplain, *abuf, *mbuf, *y, *sy, *hn, *hg;
   int *expert_id, *group_off, *sorted_row, *inv;
   float* cos_t[16]; float* sin_t[16];
 };
@@ -101,6 +110,8 @@ static size_t carve(const tha_hyb_model_t* m, int R, int n_want, char* base, Ste
   Carver c{base};
   const size_t W = m->width, es = m->dtype == THA_DT_BF16 ? 2 : 4;
   size_t n_in = 0, qd = 0, av = 0, mv = 0, cc = 0, dd = 0, dg = 0, gu = 0, ff = 0, sff = 0, top = 0, ne = 0;
+  size_t n_in2 = 0, qr = 0, qf = 0, qp = 0;
+  bool norm2 = false;
   for (int i = 0; i < m->n_layers; i++) {
     const tha_hyb_layer_t& L = m->layers[i];
     n_in = max(n_in, (size_t)L.n_in);
@@ -108,23 +119,42 @@ static size_t carve(const tha_hyb_model_t* m, int R, int n_want, char* base, Ste
       qd = max(qd, (size_t)L.attn.heads * L.attn.dim);
       av = max(av, (size_t)L.attn.heads * L.attn.vdim);
       mv = max(mv, (size_t)L.mem.heads * L.mem.vdim);
-    } else {
+    } else if (L.mixer == THA_MIX_DELTA) {
       cc = max(cc, (size_t)2 * L.delta.kv_heads * L.delta.dim + (size_t)L.delta.heads * L.delta.vdim);
       dd = max(dd, (size_t)L.delta.heads * L.delta.dim);
       dg = max(dg, (size_t)L.delta.heads * L.delta.vdim);
       mv = max(mv, (size_t)L.delta.heads * L.delta.vdim);
+    } else if (L.mixer == THA_MIX_GLA) {
+      dd = max(dd, (size_t)L.gla.heads * L.gla.dim);
+      mv = max(mv, (size_t)L.gla.heads * L.gla.vdim);
+    } else if (L.mixer == THA_MIX_LATENT) {
+      const tha_latent_t& a = L.latent;
+      qr = max(qr, (size_t)a.q_rank);
+      qf = max(qf, (size_t)a.heads * (a.dim + a.rot_dim));
+      qp = max(qp, (size_t)a.heads * a.dim);
+      qd = max(qd, (size_t)a.heads * (a.kv_rank + a.rot_dim));
+      av = max(av, (size_t)a.heads * a.kv_rank);
+      mv = max(mv, (size_t)a.heads * a.vdim);
     }
-    if (L.has_ff) {
+    if (L.has_norm2) { norm2 = true; n_in2 = max(n_in2, (size_t)L.n_in2); }
+    if (L.has_ff == THA_FF_MOE) {
       top = max(top, (size_t)L.moe.top);
       ne = max(ne, (size_t)L.moe.experts);
       gu = max(gu, (size_t)L.moe.top * 2 * L.moe.ff);
       ff = max(ff, (size_t)L.moe.top * L.moe.ff);
       sff = max(sff, (size_t)L.moe.shared_ff);
+    } else if (L.has_ff == THA_FF_DENSE) {
+      sff = max(sff, (size_t)L.dense.ff);
     }
   }
   b->x = c.take<float>(R * W);
   b->h = c.take<char>(R * W * es);
   b->proj = c.take<float>(R * n_in);
+  b->h2 = c.take<char>(norm2 ? R * W * es : 0);
+  b->proj2 = c.take<float>(R * n_in2);
+  b->cq = c.take<char>(R * qr * es);
+  b->qfull = c.take<float>(R * qf);
+  b->qplain = c.take<char>(R * qp * es);
   b->q = c.take<float>(R * qd);
   b->abuf = c.take<char>(R * av * es);
   b->mbuf = c.take<char>(R * mv * es);
@@ -191,15 +221,17 @@ extern "C" int tha_hyb_step(void* stream, const tha_hyb_model_t* m, const tha_ro
   carve(m, R, n_want, sc.base, &b);
 
   if (dt == THA_DT_BF16)
-    THA_CUDA_OK(launch(hyb_embed_kernel<bf16>, dim3(R), dim3(128), 0, s, false, b.x, (const bf16*)m->embed, rows->token, W));
+    THA_CUDA_OK(launch(hyb_embed_kernel<bf16>, dim3(R), dim3(128), 0, s, false, b.x, (const bf16*)m->embed, rows->token, W, (const bf16*)m->pos_embed,
+                       rows->pos));
   else
-    THA_CUDA_OK(launch(hyb_embed_kernel<float>, dim3(R), dim3(128), 0, s, false, b.x, (const float*)m->embed, rows->token, W));
+    THA_CUDA_OK(launch(hyb_embed_kernel<float>, dim3(R), dim3(128), 0, s, false, b.x, (const float*)m->embed, rows->token, W,
+                       (const float*)m->pos_embed, rows->pos));
   for (int i = 0; i < m->n_rot; i++) HYB_OK(tha_hyb_rotary_table(stream, &m->rot[i], rows->pos, R, b.cos_t[i], b.sin_t[i]));
 
   for (int li = 0; li < m->n_layers; li++) {
     const tha_hyb_layer_t& L = m->layers[li];
     const long long ldp = L.n_in;
-    HYB_OK(tha_hyb_rmsnorm(stream, dt, b.h, b.x, L.norm1, 1.0f, m->eps, R, W, nullptr));
+    HYB_OK(tha_hyb_norm(stream, dt, b.h, b.x, &L.norm1, m->eps, R, W, nullptr));
     HYB_OK(tha_hyb_linear(stream, dt, b.proj, ldp, b.h, W, 0, nullptr, L.w_in, 0, R, L.n_in, W, nullptr, 0));
     const float* right = nullptr;
     if (L.mixer == THA_MIX_PARALLEL) {
@@ -221,15 +253,61 @@ extern "C" int tha_hyb_step(void* stream, const tha_hyb_model_t* m, const tha_ro
       HYB_OK(tha_hyb_linear(stream, dt, b.gate_raw, d.heads * d.vdim, b.proj + d.o_g1, ldp, 1, nullptr, d.w_g2, 0, R, d.heads * d.vdim, d.rank_g, nullptr, 0));
       HYB_OK(tha_hyb_delta_scan(stream, dt, &d, rows, st, b.conv, b.proj, ldp, b.dt_raw, b.gate_raw, b.oraw, b.mbuf));
       HYB_OK(tha_hyb_linear(stream, dt, b.left, W, b.mbuf, d.heads * d.vdim, 0, nullptr, d.w_o, 0, R, W, d.heads * d.vdim, nullptr, 0));
+    } else if (L.mixer == THA_MIX_GLA) {
+      const tha_gla_t& g = L.gla;
+      HYB_OK(tha_hyb_linear(stream, dt, b.dt_raw, g.heads * g.dim, b.proj + g.o_a1, ldp, 1, nullptr, g.w_a2, 0, R, g.heads * g.dim, g.rank, nullptr, 0));
+      HYB_OK(tha_hyb_gla_scan(stream, dt, &g, rows, st, b.proj, ldp, b.dt_raw, b.oraw, b.mbuf));
+      HYB_OK(tha_hyb_linear(stream, dt, b.left, W, b.mbuf, g.heads * g.vdim, 0, nullptr, g.w_o, 0, R, W, g.heads * g.vdim, nullptr, 0));
+    } else if (L.mixer == THA_MIX_LATENT) {
+      const tha_latent_t& a = L.latent;
+      const int rd = a.rot >= 0 ? m->rot[a.rot].dims : 0;
+      const float* cs = a.rot >= 0 ? b.cos_t[a.rot] : nullptr;
+      const float* sn = a.rot >= 0 ? b.sin_t[a.rot] : nullptr;
+      const int per = a.dim + a.rot_dim, DA = a.kv_rank + a.rot_dim;
+      HYB_OK(tha_hyb_latent_prepare(stream, dt, &a, rows, kv, b.proj, ldp, cs, sn, rd, b.cq));
+      HYB_OK(tha_hyb_linear(stream, dt, b.qfull, a.heads * per, b.cq, a.q_rank, 0, nullptr, a.w_uq, 0, R, a.heads * per, a.q_rank, nullptr, 0));
+      HYB_OK(tha_hyb_latent_split_q(stream, dt, &a, R, b.qfull, cs, sn, rd, b.qplain, b.q));
+      // keys absorbed into the queries: q_abs[h, 0:kv_rank] = W_uk[h]^T q_plain[h]
+      HYB_OK(tha_hyb_linear_heads(stream, dt, b.q, (long long)a.heads * DA, DA, b.qplain, (long long)a.heads * a.dim, a.dim, 0, a.w_uk_t,
+                                  (long long)a.kv_rank * a.dim, R, a.kv_rank, a.dim, a.heads));
+      // one key/value head over the cached rows [latent | rotated part]; the values are the latent itself
+      tha_attn_t at = {};
+      at.heads = a.heads; at.kv_heads = 1; at.dim = DA; at.vdim = a.kv_rank; at.rot = -1; at.unit_rms = 0; at.eps = a.eps;
+      at.scale = a.scale; at.chunk = 0; at.cache_layer = a.cache_layer;
+      tha_kv_t lkv = *kv;
+      lkv.v_pool = kv->k_pool;
+      HYB_OK(tha_hyb_attn(stream, dt, &at, rows, &lkv, b.q, b.abuf, b.split_floats ? b.split : nullptr, b.split_floats));
+      // values expanded per head: o[h] = W_uv[h] o_latent[h]
+      HYB_OK(tha_hyb_linear_heads(stream, dt, b.oraw, (long long)a.heads * a.vdim, a.vdim, b.abuf, (long long)a.heads * a.kv_rank, a.kv_rank, 0,
+                                  a.w_uv, (long long)a.vdim * a.kv_rank, R, a.vdim, a.kv_rank, a.heads));
+      HYB_OK(tha_hyb_head_gate(stream, dt, b.mbuf, b.oraw, R, a.heads, a.vdim, 0, a.eps, nullptr, 0, b.proj + a.o_g, ldp, THA_GATE_SIGMOID));
+      HYB_OK(tha_hyb_linear(stream, dt, b.left, W, b.mbuf, a.heads * a.vdim, 0, nullptr, a.w_o, 0, R, W, a.heads * a.vdim, nullptr, 0));
     } else {
       return THA_STATUS_NOT_SUPPORTED;
     }
+    // the feed-forward reads the mixer's normed input, or a second norm of the same x through its own stacked product
+    const void* hf = b.h;
+    const float* fproj = b.proj;
+    long long ldf = ldp;
+    if (L.has_norm2 && L.has_ff != THA_FF_NONE) {
+      HYB_OK(tha_hyb_norm(stream, dt, b.h2, b.x, &L.norm2, m->eps, R, W, nullptr));
+      HYB_OK(tha_hyb_linear(stream, dt, b.proj2, L.n_in2, b.h2, W, 0, nullptr, L.w_in2, 0, R, L.n_in2, W, nullptr, 0));
+      hf = b.h2; fproj = b.proj2; ldf = L.n_in2;
+    }
     int top = 0;
     const float* sdown = nullptr;
-    if (L.has_ff) {
+    const float* sgate = nullptr;
+    if (L.has_ff == THA_FF_DENSE) {
+      const tha_dense_ff_t& d = L.dense;
+      HYB_OK(tha_hyb_ff_act(stream, dt, d.act, b.sy, fproj, ldf, d.o_gate, d.o_up, R, d.ff, 0.f, 0.f));
+      HYB_OK(tha_hyb_linear(stream, dt, b.sdown, W, b.sy, d.ff, 0, nullptr, d.w_down, 0, R, W, d.ff, nullptr, 0));
+      sdown = b.sdown;
+    } else if (L.has_ff == THA_FF_MOE) {
       const tha_moe_t& e = L.moe;
       top = e.top;
-      HYB_OK(tha_hyb_moe_route(stream, &e, b.proj, ldp, R, b.expert_id, b.weight, b.group_off, b.sorted_row, b.inv));
+      const bool gated = e.act != THA_ACT_RELU2;
+      const int gw = gated ? 2 * e.ff : e.ff, col_u = gated ? e.ff : 0;   // an expert's rows of w_gate_up; where its up rows start
+      HYB_OK(tha_hyb_moe_route(stream, &e, fproj, ldf, R, b.expert_id, b.weight, b.group_off, b.sorted_row, b.inv));
       const bool per_expert = dt == THA_DT_BF16 && R >= HYB_EXPERT_LAUNCH_ROWS && (long long)R * top >= hyb_expert_rows() * e.experts &&
                               e.experts < HYB_HOST_INTS && W % 8 == 0 && e.ff % 8 == 0 && W >= 64 && e.ff >= 64;
       if (per_expert) {
@@ -237,16 +315,16 @@ extern "C" int tha_hyb_step(void* stream, const tha_hyb_model_t* m, const tha_ro
         // contiguous rows to the TMA-fed tcgen05 matmul of the bf16 path (two launches per expert that has rows)
         if (!sc.host_ints) THA_CUDA_OK(cudaMallocHost((void**)&sc.host_ints, HYB_HOST_INTS * sizeof(int)));
         THA_CUDA_OK(cudaMemcpyAsync(sc.host_ints, b.group_off, (e.experts + 1) * sizeof(int), cudaMemcpyDeviceToHost, s));
-        THA_CUDA_OK(launch(hyb_gather_rows_kernel<bf16>, dim3(R * top), dim3(128), 0, s, false, (bf16*)b.hg, (const bf16*)b.h, (const int*)b.sorted_row, W));
+        THA_CUDA_OK(launch(hyb_gather_rows_kernel<bf16>, dim3(R * top), dim3(128), 0, s, false, (bf16*)b.hg, (const bf16*)hf, (const int*)b.sorted_row, W));
         THA_CUDA_OK(cudaStreamSynchronize(s));
         const int* off = sc.host_ints;
         for (int x = 0; x < e.experts; x++) {
           const int n = off[x + 1] - off[x];
           if (n > 0)
-            HYB_OK(tha_hyb_linear(stream, dt, b.gu + (size_t)off[x] * 2 * e.ff, 2 * e.ff, (const bf16*)b.hg + (size_t)off[x] * W, W, 0, nullptr,
-                                  (const bf16*)e.w_gate_up + (size_t)x * 2 * e.ff * W, 0, n, 2 * e.ff, W, nullptr, 0));
+            HYB_OK(tha_hyb_linear(stream, dt, b.gu + (size_t)off[x] * gw, gw, (const bf16*)b.hg + (size_t)off[x] * W, W, 0, nullptr,
+                                  (const bf16*)e.w_gate_up + (size_t)x * gw * W, 0, n, gw, W, nullptr, 0));
         }
-        HYB_OK(tha_hyb_glu_clamped(stream, dt, b.y, b.gu, 2 * e.ff, 0, e.ff, R * top, e.ff, e.limit, e.alpha));
+        HYB_OK(tha_hyb_ff_act(stream, dt, e.act, b.y, b.gu, gw, 0, col_u, R * top, e.ff, e.limit, e.alpha));
         for (int x = 0; x < e.experts; x++) {
           const int n = off[x + 1] - off[x];
           if (n > 0)
@@ -254,23 +332,24 @@ extern "C" int tha_hyb_step(void* stream, const tha_hyb_model_t* m, const tha_ro
                                   (const bf16*)e.w_down + (size_t)x * W * e.ff, 0, n, W, e.ff, nullptr, 0));
         }
       } else {
-        HYB_OK(tha_hyb_linear(stream, dt, b.gu, 2 * e.ff, b.h, W, 0, b.sorted_row, e.w_gate_up, (long long)2 * e.ff * W, R * top, 2 * e.ff, W,
+        HYB_OK(tha_hyb_linear(stream, dt, b.gu, gw, hf, W, 0, b.sorted_row, e.w_gate_up, (long long)gw * W, R * top, gw, W,
                               b.group_off, e.experts));
-        HYB_OK(tha_hyb_glu_clamped(stream, dt, b.y, b.gu, 2 * e.ff, 0, e.ff, R * top, e.ff, e.limit, e.alpha));
+        HYB_OK(tha_hyb_ff_act(stream, dt, e.act, b.y, b.gu, gw, 0, col_u, R * top, e.ff, e.limit, e.alpha));
         HYB_OK(tha_hyb_linear(stream, dt, b.down, W, b.y, e.ff, 0, nullptr, e.w_down, (long long)W * e.ff, R * top, W, e.ff, b.group_off, e.experts));
       }
       if (e.shared_ff > 0) {
-        HYB_OK(tha_hyb_glu_clamped(stream, dt, b.sy, b.proj, ldp, e.o_sgate, e.o_sup, R, e.shared_ff, e.shared_limit, e.alpha));
+        HYB_OK(tha_hyb_ff_act(stream, dt, e.act, b.sy, fproj, ldf, e.o_sgate, e.o_sup, R, e.shared_ff, e.shared_limit, e.alpha));
         HYB_OK(tha_hyb_linear(stream, dt, b.sdown, W, b.sy, e.shared_ff, 0, nullptr, e.w_sdown, 0, R, W, e.shared_ff, nullptr, 0));
         sdown = b.sdown;
+        if (e.shared_scaled) sgate = fproj + e.o_sscale;
       }
     }
     THA_CUDA_OK(launch(hyb_finish_kernel, dim3(R), dim3(128), 0, s, false, b.x, W, m->eps, (const float*)b.left, right, L.left_out, L.right_out, top,
-                       (const float*)b.weight, (const int*)b.inv, (const float*)b.down, sdown,
+                       (const float*)b.weight, (const int*)b.inv, (const float*)b.down, sdown, sgate, ldf, L.scale_mix, L.scale_ff,
                        taps ? taps + (size_t)li * R * W : (float*)nullptr));
   }
   if (n_want > 0 && logits) {
-    HYB_OK(tha_hyb_rmsnorm(stream, dt, b.hn, b.x, m->final_norm, 1.0f, m->eps, n_want, W, want_rows));
+    HYB_OK(tha_hyb_norm(stream, dt, b.hn, b.x, &m->final_norm, m->eps, n_want, W, want_rows));
     HYB_OK(tha_hyb_linear(stream, dt, logits, m->vocab, b.hn, W, 0, nullptr, m->head, 0, n_want, m->vocab, W, nullptr, 0));
     if (m->logit_softcap > 0.f) {
       const size_t n = (size_t)n_want * m->vocab;

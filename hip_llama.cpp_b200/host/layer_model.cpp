@@ -15,6 +15,7 @@
 #include "tha_b200.h"
 
 void register_timerax();   // host/arch_timerax.cpp
+void register_numizen();   // host/arch_numizen.cpp
 
 // ---- registry -----------------------------------------------------------------------------------------------------
 static std::vector<ArchitectureEntry>& registry() {
@@ -26,6 +27,7 @@ static void register_builtin() {
   std::call_once(once, [] {
     registry().push_back({"llama2", ModelFamily::Llama2Checkpoint, nullptr});   // llama2.c v0 / v2 checkpoint files (host/utils.cpp)
     register_timerax();
+    register_numizen();
   });
 }
 void register_architecture(const ArchitectureEntry& e) {
@@ -224,15 +226,85 @@ LayerModel* LayerModel::build(const LayerProgramSpec& spec, const SafeTensors& f
       s.add(name, rows);
       return m->upload(s.data(), s.bytes());
     };
+    // a norm over the width by name: the weight, and for the dynamic tanh its bias and scalar beside it
+    auto norm = [&](const std::string& name) -> tha_norm_t {
+      tha_norm_t n = {};
+      n.kind = spec.norm_kind;
+      n.w = vec(name, W);
+      n.w_offset = 1.0f;
+      if (spec.norm_kind == THA_NORM_DYT) {
+        n.w_offset = 0.0f;
+        n.b = vec(name + ".b", W);
+        std::vector<float> a;
+        file.read_f32(name + ".alpha", &a);
+        if (a.size() != 1) throw std::runtime_error("tensor '" + name + ".alpha' must be one number");
+        n.alpha = a[0];
+      }
+      return n;
+    };
+    // the rotary table of a setting (shared between layers with the same one): inverse frequencies in float64,
+    // base^(-2i/dims), interpolated between the original and the stretched scale
+    auto rotary = [&](const RotarySpec& rs) -> int {
+      size_t r = 0;
+      while (r < m->rot_specs_.size() && !(m->rot_specs_[r] == rs)) r++;
+      if (r == m->rot_specs_.size()) {
+        const int dims = rs.dims, half = dims / 2;
+        std::vector<double> f(half);
+        for (int i = 0; i < half; i++) f[i] = pow(rs.base, -2.0 * i / dims);
+        float mag = 1.0f;
+        if (rs.yarn) {
+          auto where = [&](double turns) { return dims * log(rs.original / (2.0 * M_PI * turns)) / (2.0 * log(rs.base)); };
+          const double lo = fmax(floor(where(rs.fast)), 0.0), hi = fmin(ceil(where(rs.slow)), dims - 1.0);
+          for (int i = 0; i < half; i++) {
+            const double ramp = fmin(fmax((i - lo) / fmax(hi - lo, 0.001), 0.0), 1.0);
+            f[i] = f[i] / rs.factor * ramp + f[i] * (1.0 - ramp);
+          }
+          mag = (float)(0.1 * log(rs.factor) + 1.0);
+        }
+        tha_rotary_t R;
+        R.inv_freq = (const double*)m->upload(f.data(), f.size() * 8);
+        R.dims = dims;
+        R.mag = mag;
+        m->rot_.push_back(R);
+        m->rot_specs_.push_back(rs);
+      }
+      return (int)r;
+    };
     m->layers_.resize(spec.layers.size());
     long long state = 0;
     for (size_t li = 0; li < spec.layers.size(); li++) {
       const LayerSpec& ls = spec.layers[li];
       tha_hyb_layer_t& L = m->layers_[li];
+      if (ls.same_weights_as >= 0) {
+        // another run of an earlier entry: the same device weights, a cache layer and state of its own
+        if ((size_t)ls.same_weights_as >= li) throw std::runtime_error("a repeated layer must follow the layer it repeats");
+        L = m->layers_[ls.same_weights_as];
+        if (L.mixer == THA_MIX_PARALLEL) {
+          L.attn.cache_layer = m->n_cache_layers_++;
+          L.mem.state_off = state;
+          state += (long long)L.mem.heads * ((long long)L.mem.dim * L.mem.vdim + L.mem.dim + 1);
+        } else if (L.mixer == THA_MIX_DELTA) {
+          L.delta.state_off = state;
+          state += (long long)L.delta.heads * L.delta.dim * L.delta.vdim;
+          L.delta.conv_state_off = state;
+          state += (2ll * L.delta.kv_heads * L.delta.dim + (long long)L.delta.heads * L.delta.vdim) * (L.delta.taps - 1);
+        } else if (L.mixer == THA_MIX_GLA) {
+          L.gla.state_off = state;
+          state += (long long)L.gla.heads * L.gla.dim * L.gla.vdim;
+        } else if (L.mixer == THA_MIX_LATENT) {
+          L.latent.cache_layer = m->n_cache_layers_++;
+        }
+        continue;
+      }
       memset(&L, 0, sizeof(L));
       L.mixer = ls.mixer;
-      L.norm1 = vec(ls.norm1, W);
+      L.norm1 = norm(ls.norm1);
+      if (!ls.scale_mix.empty()) L.scale_mix = vec(ls.scale_mix, W);
+      if (!ls.scale_ff.empty() && ls.has_ff) L.scale_ff = vec(ls.scale_ff, W);
       Stack in(file, dtype, W);
+      Stack in2(file, dtype, W);                       // what reads the second norm
+      const bool two = !ls.norm2.empty() && ls.has_ff;
+      Stack& fin = two ? in2 : in;                     // where the feed-forward's input matrices go
       if (ls.mixer == THA_MIX_PARALLEL) {
         const AttnSpec& a = ls.attn;
         if (a.heads < 1 || a.kv_heads < 1 || a.heads % a.kv_heads) throw std::runtime_error("attention: heads must be a multiple of kv_heads");
@@ -242,31 +314,7 @@ LayerModel* LayerModel::build(const LayerProgramSpec& spec, const SafeTensors& f
         A.rot = -1;
         if (a.rotary && a.rot.dims > 0) {
           if (a.rot.dims > a.dim || (a.rot.dims & 1)) throw std::runtime_error("attention: rotated dimensions must be even and at most dim");
-          size_t r = 0;
-          while (r < m->rot_specs_.size() && !(m->rot_specs_[r] == a.rot)) r++;
-          if (r == m->rot_specs_.size()) {
-            // inverse frequencies in float64: base^(-2i/dims), interpolated between the original and the stretched scale
-            const int dims = a.rot.dims, half = dims / 2;
-            std::vector<double> f(half);
-            for (int i = 0; i < half; i++) f[i] = pow(a.rot.base, -2.0 * i / dims);
-            float mag = 1.0f;
-            if (a.rot.yarn) {
-              auto where = [&](double turns) { return dims * log(a.rot.original / (2.0 * M_PI * turns)) / (2.0 * log(a.rot.base)); };
-              const double lo = fmax(floor(where(a.rot.fast)), 0.0), hi = fmin(ceil(where(a.rot.slow)), dims - 1.0);
-              for (int i = 0; i < half; i++) {
-                const double ramp = fmin(fmax((i - lo) / fmax(hi - lo, 0.001), 0.0), 1.0);
-                f[i] = f[i] / a.rot.factor * ramp + f[i] * (1.0 - ramp);
-              }
-              mag = (float)(0.1 * log(a.rot.factor) + 1.0);
-            }
-            tha_rotary_t R;
-            R.inv_freq = (const double*)m->upload(f.data(), f.size() * 8);
-            R.dims = dims;
-            R.mag = mag;
-            m->rot_.push_back(R);
-            m->rot_specs_.push_back(a.rot);
-          }
-          A.rot = (int)r;
+          A.rot = rotary(a.rot);
         }
         A.cache_layer = m->n_cache_layers_++;
         m->kv_dim_ = std::max(m->kv_dim_, std::max(a.kv_heads * a.dim, a.kv_heads * a.vdim));
@@ -324,20 +372,104 @@ LayerModel* LayerModel::build(const LayerProgramSpec& spec, const SafeTensors& f
         state += (long long)d.heads * d.dim * d.vdim;
         D.conv_state_off = state;
         state += (2 * cq + cv) * (d.taps - 1);
+      } else if (ls.mixer == THA_MIX_GLA) {
+        const GlaSpec& g = ls.gla;
+        if (g.heads < 1 || g.dim < 1 || g.vdim < 1 || !(g.tau > 0.f)) throw std::runtime_error("gated linear attention: heads, dim, vdim and tau must be positive");
+        if (g.dim > 512) throw std::runtime_error("gated linear attention: more than 512 key channels per head are not served");
+        tha_gla_t& G = L.gla;
+        G.heads = g.heads; G.dim = g.dim; G.vdim = g.vdim; G.tau = g.tau; G.eps = spec.eps;
+        const TensorInfo& a1 = file.info(g.a1);
+        if (a1.shape.size() != 2) throw std::runtime_error("gated linear attention: the decay projection must be a matrix");
+        G.rank = (int)a1.shape[0];
+        G.o_q = in.add(g.q, (long long)g.heads * g.dim);
+        G.o_k = in.add(g.k, (long long)g.heads * g.dim);
+        G.o_v = in.add(g.v, (long long)g.heads * g.vdim);
+        G.o_g = in.add(g.g, (long long)g.heads * g.vdim);
+        G.o_a1 = in.add(g.a1, G.rank);
+        G.w_a2 = mat(g.a2, (long long)g.heads * g.dim, G.rank);
+        G.b_a2 = vec(g.a2_b, (size_t)g.heads * g.dim);
+        G.norm = vec(g.norm, g.vdim);
+        G.w_o = mat(g.o, W, g.heads * g.vdim);
+        G.state_off = state;
+        state += (long long)g.heads * g.dim * g.vdim;
+      } else if (ls.mixer == THA_MIX_LATENT) {
+        const LatentSpec& a = ls.latent;
+        if (a.heads < 1 || a.dim < 1 || a.vdim < 1 || a.q_rank < 1 || a.kv_rank < 1 || a.rot_dim < 0)
+          throw std::runtime_error("latent attention: heads, dim, vdim, q_rank and kv_rank must be positive");
+        tha_latent_t& A = L.latent;
+        A.heads = a.heads; A.dim = a.dim; A.rot_dim = a.rot_dim; A.vdim = a.vdim; A.q_rank = a.q_rank; A.kv_rank = a.kv_rank;
+        A.eps = spec.eps; A.scale = a.scale;
+        A.rot = -1;
+        if (a.rotary && a.rot.dims > 0 && a.rot_dim > 0) {
+          if (a.rot.dims > a.rot_dim || (a.rot.dims & 1)) throw std::runtime_error("latent attention: rotated dimensions must be even and at most rot_dim");
+          A.rot = rotary(a.rot);
+        }
+        A.cache_layer = m->n_cache_layers_++;
+        m->kv_dim_ = std::max(m->kv_dim_, a.kv_rank + a.rot_dim);
+        A.o_dq = in.add(a.dq, a.q_rank);
+        A.o_dkv = in.add(a.dkv, (long long)a.kv_rank + a.rot_dim);
+        A.o_g = in.add(a.g, (long long)a.heads * a.vdim);
+        A.q_norm = vec(a.dq_norm, a.q_rank);
+        A.kv_norm = vec(a.dkv_norm, a.kv_rank);
+        A.w_uq = mat(a.uq, (long long)a.heads * (a.dim + a.rot_dim), a.q_rank);
+        {
+          // W_uk [heads * dim, kv_rank] -> per head its transpose [kv_rank, dim]: the matrix that carries a head's plain
+          // query part into the latent space
+          const TensorInfo& t = file.info(a.uk);
+          if (t.shape.size() != 2 || t.shape[0] != (long long)a.heads * a.dim || t.shape[1] != a.kv_rank)
+            throw std::runtime_error("tensor '" + a.uk + "': shape does not fit [heads * dim, kv_rank]");
+          const size_t n = (size_t)a.heads * a.dim * a.kv_rank;
+          if (dtype == THA_DT_BF16) {
+            std::vector<uint16_t> src, dst(n);
+            file.read_bf16(a.uk, &src);
+            for (int h = 0; h < a.heads; h++)
+              for (int d = 0; d < a.dim; d++)
+                for (int c = 0; c < a.kv_rank; c++) dst[((size_t)h * a.kv_rank + c) * a.dim + d] = src[((size_t)h * a.dim + d) * a.kv_rank + c];
+            A.w_uk_t = m->upload(dst.data(), n * 2);
+          } else {
+            std::vector<float> src, dst(n);
+            file.read_f32(a.uk, &src);
+            for (int h = 0; h < a.heads; h++)
+              for (int d = 0; d < a.dim; d++)
+                for (int c = 0; c < a.kv_rank; c++) dst[((size_t)h * a.kv_rank + c) * a.dim + d] = src[((size_t)h * a.dim + d) * a.kv_rank + c];
+            A.w_uk_t = m->upload(dst.data(), n * 4);
+          }
+        }
+        A.w_uv = mat(a.uv, (long long)a.heads * a.vdim, a.kv_rank);
+        A.w_o = mat(a.o, W, a.heads * a.vdim);
       } else {
         throw std::runtime_error("unknown mixer kind");
       }
-      L.has_ff = ls.has_ff ? 1 : 0;
-      if (ls.has_ff) {
+      L.has_ff = ls.has_ff ? ls.ff_kind : THA_FF_NONE;
+      if (two) { L.has_norm2 = 1; L.norm2 = norm(ls.norm2); }
+      if (ls.has_ff && ls.ff_kind == THA_FF_DENSE) {
+        const DenseSpec& d = ls.dense;
+        if (d.ff < 1) throw std::runtime_error("dense feed-forward: ff must be positive");
+        L.dense.ff = d.ff;
+        L.dense.act = d.act;
+        L.dense.o_gate = fin.add(d.gate, d.ff);
+        L.dense.o_up = fin.add(d.up, d.ff);
+        L.dense.w_down = mat(d.down, W, d.ff);
+      } else if (ls.has_ff) {
         const MoeSpec& e = ls.moe;
         if (e.top < 1 || e.top > e.experts || e.top > 32) throw std::runtime_error("mixture of experts: 1 <= top <= min(experts, 32)");
         tha_moe_t& E = L.moe;
         E.experts = e.experts; E.top = e.top; E.ff = e.ff; E.limit = e.limit; E.alpha = e.alpha;
-        E.o_router = in.add(e.router, e.experts);
+        E.act = e.act; E.route = e.route;
+        if (e.route == THA_ROUTE_SOFTMAX_GROUPS) {
+          const int groups = e.groups > 1 ? e.groups : 1, keep = e.groups > 1 ? e.keep_groups : 1;
+          if (groups > 32 || e.experts % groups || keep < 1 || keep > groups || e.experts > 4096)
+            throw std::runtime_error("mixture of experts: groups must divide the experts (at most 32 groups, 4096 experts), 1 <= keep <= groups");
+          if ((long long)keep * (e.experts / groups) < e.top) throw std::runtime_error("mixture of experts: the kept groups hold fewer experts than 'top'");
+          E.groups = groups; E.keep_groups = keep;
+          if (!e.correction.empty() && file.has(e.correction)) E.correction = vec(e.correction, e.experts);
+        }
+        const bool gated = e.act != THA_ACT_RELU2;
+        E.o_router = fin.add(e.router, e.experts);
         Stack gu(file, dtype, W), dn(file, dtype, e.ff);
         for (int x = 0; x < e.experts; x++) {
           const std::string p = e.prefix + "e" + std::to_string(x) + ".";
-          gu.add(p + "gate", e.ff);
+          if (gated) gu.add(p + "gate", e.ff);
           gu.add(p + "up", e.ff);
           dn.add(p + "down", W);
         }
@@ -346,13 +478,18 @@ LayerModel* LayerModel::build(const LayerProgramSpec& spec, const SafeTensors& f
         E.shared_ff = e.shared_ff;
         E.shared_limit = e.shared_limit;
         if (e.shared_ff > 0) {
-          E.o_sgate = in.add(e.s_gate, e.shared_ff);
-          E.o_sup = in.add(e.s_up, e.shared_ff);
+          if (gated) E.o_sgate = fin.add(e.s_gate, e.shared_ff);
+          E.o_sup = fin.add(e.s_up, e.shared_ff);
           E.w_sdown = mat(e.s_down, W, e.shared_ff);
+          if (!e.s_scale.empty()) { E.shared_scaled = 1; E.o_sscale = fin.add(e.s_scale, 1); }
         }
       }
       L.n_in = in.rows;
       L.w_in = m->upload(in.data(), in.bytes());
+      if (two) {
+        L.n_in2 = in2.rows;
+        L.w_in2 = m->upload(in2.data(), in2.bytes());
+      }
     }
     m->state_floats_ = state > 0 ? state : 1;
     if (m->rot_.size() > 16) throw std::runtime_error("more than 16 distinct rotary tables");
@@ -364,7 +501,12 @@ LayerModel* LayerModel::build(const LayerProgramSpec& spec, const SafeTensors& f
     M.eps = spec.eps;
     M.logit_softcap = spec.logit_softcap;
     M.embed = mat(spec.embed, spec.vocab, W);
-    M.final_norm = vec(spec.final_norm, W);
+    if (!spec.pos_embed.empty()) {
+      if (spec.max_positions < 1) throw std::runtime_error("a position table needs max_positions");
+      M.pos_embed = mat(spec.pos_embed, spec.max_positions, W);
+      M.max_positions = spec.max_positions;
+    }
+    M.final_norm = norm(spec.final_norm);
     M.head = mat(spec.head, spec.vocab, W);
     M.layers = m->layers_.data();
     M.n_rot = (int)m->rot_.size();

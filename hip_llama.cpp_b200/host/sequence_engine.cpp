@@ -82,6 +82,7 @@ bool SequenceEngine::run(const std::vector<StepEntry>& entries, bool to_host, st
       if (w < 0 || w >= (int)e.tokens.size()) return fail("wanted place out of range");
     const int last = filled_[s] + (int)e.tokens.size() - 1;
     if (last >= bm_.nrow_blocks * bm_.block_size) return fail("request '" + e.id + "' is longer than the cache can address");
+    if (model_->max_positions() > 0 && last >= model_->max_positions()) return fail("request '" + e.id + "' is longer than the model's position table");
     if (!bm_.ensure_position(s, last)) return fail("cache pool exhausted");
     live.push_back(&e);
     R += e.tokens.size();

@@ -43,15 +43,44 @@ struct DeltaSpec {
   int heads = 0, kv_heads = 0, dim = 0, vdim = 0, taps = 1;
   std::string q, k, v, q_conv, k_conv, v_conv, b, a_log, norm, a1, a2, dt_bias, g1, g2, o;
 };
+struct GlaSpec {
+  int heads = 0, dim = 0, vdim = 0;
+  float tau = 1.0f;
+  std::string q, k, v, g, o, norm, a1, a2, a2_b;   // the rank of a1 / a2 is read from the tensors
+};
+struct LatentSpec {
+  int heads = 0, dim = 0, rot_dim = 0, vdim = 0, q_rank = 0, kv_rank = 0;
+  bool rotary = false;
+  RotarySpec rot;
+  float scale = 1.0f;
+  std::string dq, dq_norm, uq, dkv, dkv_norm, uk, uv, g, o;
+};
+struct DenseSpec {
+  int ff = 0, act = THA_ACT_GELU_TANH_GLU;
+  std::string gate, up, down;
+};
 struct MoeSpec {
   int experts = 0, top = 0, ff = 0, shared_ff = 0;
   float limit = 0.f, shared_limit = 0.f, alpha = 1.702f;
-  std::string router, prefix;            // expert e's tensors: prefix + "e<e>.gate" / ".up" / ".down"
+  std::string router, prefix;            // expert e's tensors: prefix + "e<e>.gate" / ".up" / ".down" (ungated: no ".gate")
   std::string s_gate, s_up, s_down;
+  int act = THA_ACT_GLU_CLAMPED, route = THA_ROUTE_TOPK_SOFTMAX;
+  std::string correction;                // THA_ROUTE_SOFTMAX_GROUPS
+  int groups = 0, keep_groups = 0;
+  std::string s_scale;                   // [1, width]: the shared expert is multiplied by sigmoid of this product; empty: none
 };
 struct LayerSpec {
   int mixer = THA_MIX_PARALLEL;
+  // >= 0: this entry runs the weights of that earlier entry once more (a looped segment) with a cache layer and state of
+  // its own; the other fields are copies
+  int same_weights_as = -1;
   std::string norm1;
+  std::string norm2;                     // a second norm of the same x for the feed-forward; empty: it reads norm1's output
+  std::string scale_mix, scale_ff;       // layer scales [width]; empty: none
+  GlaSpec gla;
+  LatentSpec latent;
+  int ff_kind = THA_FF_MOE;              // with has_ff
+  DenseSpec dense;
   AttnSpec attn;
   MemSpec mem;
   std::string left_out, right_out;
@@ -62,6 +91,11 @@ struct LayerSpec {
 struct LayerProgramSpec {
   int width = 0, vocab = 0;
   float eps = 1e-5f, logit_softcap = 0.f;
+  // every norm over the width (the layers' and the final one): THA_NORM_RMS with weights stored around zero, or
+  // THA_NORM_DYT with "<name>.alpha" (a scalar) and "<name>.b" beside the weight
+  int norm_kind = THA_NORM_RMS;
+  std::string pos_embed;                 // learned position vectors [max_positions, width]; empty: none
+  int max_positions = 0;                 // 0: no limit from the model
   std::string embed, final_norm, head;
   std::vector<LayerSpec> layers;
 };
@@ -112,6 +146,7 @@ class LayerModel {
   const tha_hyb_model_t* device_model() const { return &model_; }
   const LayerProgramSpec& spec() const { return spec_; }
   int vocab() const { return spec_.vocab; }
+  int max_positions() const { return spec_.pos_embed.empty() ? 0 : spec_.max_positions; }   // 0: no limit
   int n_cache_layers() const { return n_cache_layers_; }
   int kv_dim() const { return kv_dim_; }                    // widest K or V row (floats)
   long long state_floats() const { return state_floats_; }  // recurrent state of one sequence

@@ -32,6 +32,26 @@ extern "C" {
 
 #define THA_MIX_PARALLEL 0 /* softmax attention and a matrix memory side by side, outputs normed and averaged */
 #define THA_MIX_DELTA 1    /* gated delta rule with per-channel decay */
+#define THA_MIX_GLA 2      /* gated linear attention: decayed outer-product memory, decay per key channel */
+#define THA_MIX_LATENT 3   /* softmax attention whose keys and values are expanded from one cached low-rank latent */
+
+#define THA_NORM_RMS 0     /* x / sqrt(mean(x^2) + eps) * (w_offset + w) */
+#define THA_NORM_DYT 1     /* tanh(alpha * x) * w + b: element-wise, no statistics */
+
+#define THA_FF_NONE 0
+#define THA_FF_MOE 1
+#define THA_FF_DENSE 2
+
+#define THA_ACT_GLU_CLAMPED 0 /* g' = min(g, limit), u' = clamp(u, +-limit): g' sigmoid(alpha g') (u' + 1) */
+#define THA_ACT_RELU2 1       /* max(u, 0)^2, no gate */
+#define THA_ACT_GELU_TANH_GLU 2 /* gelu(g) u, gelu in its tanh form */
+
+#define THA_ROUTE_TOPK_SOFTMAX 0    /* the top logits, softmax over the chosen */
+#define THA_ROUTE_SOFTMAX_GROUPS 1  /* softmax over all experts; choice by score + correction inside the best groups of
+                                       neighbouring experts; weights = the chosen scores (uncorrected) over their sum */
+
+#define THA_GATE_SIGMOID 0
+#define THA_GATE_SILU 1
 
 /* The rows of one step.  Rows of a sequence are consecutive and in ascending position. */
 typedef struct {
@@ -68,6 +88,15 @@ typedef struct {
   int dims;               /* rotated dimensions of a head (pairs 2i, 2i+1), the rest pass unchanged */
   float mag;
 } tha_rotary_t;
+
+/* A norm over the width. */
+typedef struct {
+  int kind;          /* THA_NORM_* */
+  const float* w;    /* [width] */
+  const float* b;    /* [width], THA_NORM_DYT */
+  float w_offset;    /* THA_NORM_RMS: 1 when the weight is stored around zero */
+  float alpha;       /* THA_NORM_DYT */
+} tha_norm_t;
 
 /* Softmax attention over the cache.  A query at position p sees the keys j <= p with
  * floor(j / chunk) == floor(p / chunk) when chunk > 0, every j <= p otherwise. */
@@ -113,6 +142,48 @@ typedef struct {
   long long state_off, conv_state_off;
 } tha_delta_t;
 
+/* Gated linear attention.  Per head S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T (q_t / sqrt(dim)), with the decay
+ * a = sigmoid(z)^(1/tau) per key channel, z = W_a2 (W_a1 h) + b_a2.  The read-out is divided by its root mean square per
+ * head, weighted (norm, [vdim], shared by the heads) and gated by silu(W_g h).  State per head: S [dim, vdim]. */
+typedef struct {
+  int heads, dim, vdim, rank;
+  float tau, eps;
+  int o_q, o_k, o_v, o_g, o_a1; /* columns of the stacked input projection */
+  const void* w_a2;    /* [heads * dim, rank] */
+  const float* b_a2;   /* [heads * dim] */
+  const float* norm;   /* [vdim] */
+  const void* w_o;     /* [width, heads * vdim] */
+  long long state_off;
+} tha_gla_t;
+
+/* Latent attention.  Queries: c_q = rmsnorm(W_dq h) * q_norm, q = W_uq c_q, per head [dim plain | rot_dim rotated].
+ * Keys and values: W_dkv h = [kv_rank | rot_dim]; c = rmsnorm(first part) * kv_norm is the cached latent, the second part
+ * (rotated) is one key part shared by all heads; per head k = W_uk c, v = W_uv c.  Only [c | rotated part] is cached
+ * (kv_rank + rot_dim floats per position, in the K pool).  The score q_plain . W_uk c equals (W_uk^T q_plain) . c, so the
+ * kernels attend with absorbed queries [W_uk^T q_plain | q_rot] over the cached rows as ONE key/value head of
+ * kv_rank + rot_dim channels whose values are the latent itself, and expand the result with W_uv afterwards.
+ * Output gate sigmoid(W_g h) on the concatenated heads. */
+typedef struct {
+  int heads, dim, rot_dim, vdim, q_rank, kv_rank;
+  int rot;            /* index into the model's rotary tables (dims <= rot_dim), -1: none */
+  float eps, scale;
+  int cache_layer;
+  int o_dq, o_dkv, o_g; /* columns of the stacked input projection: q_rank, kv_rank + rot_dim, heads * vdim */
+  const float* q_norm;  /* [q_rank] */
+  const float* kv_norm; /* [kv_rank] */
+  const void* w_uq;     /* [heads * (dim + rot_dim), q_rank] */
+  const void* w_uk_t;   /* [heads][kv_rank, dim]: W_uk of each head, transposed */
+  const void* w_uv;     /* [heads][vdim, kv_rank] */
+  const void* w_o;      /* [width, heads * vdim] */
+} tha_latent_t;
+
+/* Dense gated feed-forward: W_down act(W_gate h, W_up h). */
+typedef struct {
+  int ff, act;
+  int o_gate, o_up;     /* columns of the feed-forward's stacked input projection */
+  const void* w_down;   /* [width, ff] */
+} tha_dense_ff_t;
+
 /* Mixture of experts with clamped gated activation: g = min(gate, limit), u = clamp(up, -limit, limit),
  * y = g * sigmoid(alpha * g) * (u + 1).  Router: top-k logits, softmax over the chosen.  Optional shared expert. */
 typedef struct {
@@ -125,20 +196,38 @@ typedef struct {
   float shared_limit;
   int o_sgate, o_sup;
   const void* w_sdown;   /* [width, shared_ff] */
+  /* zero-initialised, the fields below keep the behaviour described above */
+  int act;               /* THA_ACT_*; ungated activations: w_gate_up is [experts][ff, width] (up rows only) */
+  int route;             /* THA_ROUTE_* */
+  const float* correction; /* [experts], THA_ROUTE_SOFTMAX_GROUPS: added to the scores for the choice only */
+  int groups, keep_groups; /* groups <= 1: every expert can be chosen */
+  int shared_scaled;     /* 1: the shared expert's output is multiplied by sigmoid of column o_sscale (one number per row) */
+  int o_sscale;
 } tha_moe_t;
 
 typedef struct {
   int mixer;            /* THA_MIX_* */
-  const float* norm1;   /* [width] stored around zero: the factor is 1 + w */
+  tha_norm_t norm1;     /* the mixer's input norm (and the feed-forward's, unless norm2 is set) */
   const void* w_in;     /* every matrix that reads the normed input, stacked: [n_in, width] */
   int n_in;
+  /* A second norm of the same x for the feed-forward (has_norm2): its matrices are stacked in w_in2 [n_in2, width] and
+   * the column offsets of moe / dense refer to that product; without it they refer to w_in. */
+  int has_norm2;
+  tha_norm_t norm2;
+  const void* w_in2;
+  int n_in2;
+  const float* scale_mix; /* [width] layer scale on the mixer's result, NULL: none */
+  const float* scale_ff;  /* [width] layer scale on the feed-forward's result, NULL: none */
   tha_attn_t attn;      /* THA_MIX_PARALLEL */
   tha_mem_t mem;        /* THA_MIX_PARALLEL */
   const float* left_out;  /* [width] weights of the two sides' output norms */
   const float* right_out;
   tha_delta_t delta;    /* THA_MIX_DELTA */
-  int has_ff;
-  tha_moe_t moe;
+  tha_gla_t gla;        /* THA_MIX_GLA */
+  tha_latent_t latent;  /* THA_MIX_LATENT */
+  int has_ff;           /* THA_FF_* */
+  tha_moe_t moe;        /* THA_FF_MOE */
+  tha_dense_ff_t dense; /* THA_FF_DENSE */
 } tha_hyb_layer_t;
 
 typedef struct {
@@ -147,9 +236,13 @@ typedef struct {
   float eps;
   float logit_softcap;  /* 0: none */
   const void* embed;    /* [vocab, width] */
-  const float* final_norm;
+  const void* pos_embed; /* [max_positions, width] learned position vectors added to the embedding, NULL: none */
+  int max_positions;
+  tha_norm_t final_norm;
   const void* head;     /* [vocab, width] */
-  const tha_hyb_layer_t* layers; /* host array */
+  /* host array of the layer RUNS in execution order: a layer that a model runs several times (a looped segment) appears
+   * once per run with the same weight pointers and a cache layer / state offset of its own */
+  const tha_hyb_layer_t* layers;
   int n_rot;
   const tha_rotary_t* rot;       /* host array */
 } tha_hyb_model_t;
@@ -165,12 +258,19 @@ int tha_hyb_step(void* stream, const tha_hyb_model_t* m, const tha_rows_t* rows,
  * out is dtype-typed (bf16 / fp32) */
 int tha_hyb_rmsnorm(void* stream, int dtype, void* out, const float* x, const float* w, float w_offset, float eps,
                     int n_rows, int width, const int* rows_idx);
+/* the norm `n` of rows of x (picked through rows_idx when not NULL); out is dtype-typed */
+int tha_hyb_norm(void* stream, int dtype, void* out, const float* x, const tha_norm_t* n, float eps, int n_rows, int width,
+                 const int* rows_idx);
 /* C[m, 0:N] = A[row(m), 0:K] . W_g[0:N, 0:K]^T, fp32 out.  a_f32: A is fp32 (else dtype-typed).  gather: row(m) =
  * a_rows[m] (NULL: m).  Groups: rows group_off[g] .. group_off[g+1]-1 use the matrix W + g * w_group_stride elements
  * (group_off NULL: one group of M rows). */
 int tha_hyb_linear(void* stream, int dtype, float* C, long long ldc, const void* A, long long lda, int a_f32,
                    const int* a_rows, const void* W, long long w_group_stride, int M, int N, int K,
                    const int* group_off, int n_groups);
+/* One product per head: C[m, h * c_hs + n] = sum_k A[m, h * a_hs + k] * W[h * w_hs + n * K + k], n < N, k < K, fp32 out.
+ * a_f32: A is fp32 (else dtype-typed). */
+int tha_hyb_linear_heads(void* stream, int dtype, float* C, long long ldc, long long c_hs, const void* A, long long lda,
+                         long long a_hs, int a_f32, const void* W, long long w_hs, int M, int N, int K, int heads);
 /* cos / sin [n_rows, dims/2] of the rows' positions */
 int tha_hyb_rotary_table(void* stream, const tha_rotary_t* rot, const int* pos, int n_rows, float* cos_out, float* sin_out);
 /* rotate q and k, unit-rms them, write k and v to the cache rows of (slot, pos), q to q_out [n_rows, heads * dim] */
@@ -197,6 +297,24 @@ int tha_hyb_conv_silu(void* stream, const tha_rows_t* rows, const tha_state_stor
 int tha_hyb_delta_scan(void* stream, int dtype, const tha_delta_t* d, const tha_rows_t* rows, const tha_state_store_t* st,
                        const float* qkv, float* proj, long long ldp, float* dt_raw, const float* gate_raw,
                        float* o_raw, void* out);
+/* latent attention, before the query expansion: cq (dtype-typed [n_rows, q_rank]) = rmsnorm of the q_rank columns at o_dq
+ * times q_norm; the cache row of (slot, pos) in the K pool = [rmsnorm of the kv_rank columns at o_dkv times kv_norm |
+ * the following rot_dim columns, rotated] */
+int tha_hyb_latent_prepare(void* stream, int dtype, const tha_latent_t* a, const tha_rows_t* rows, const tha_kv_t* kv,
+                           const float* proj, long long ldp, const float* cos_t, const float* sin_t, int rot_dims, void* cq);
+/* latent attention, after the query expansion qfull fp32 [n_rows, heads * (dim + rot_dim)]: the plain parts go to
+ * q_plain (dtype-typed [n_rows, heads * dim]), the rotated parts to columns kv_rank.. of q_abs (fp32 [n_rows, heads *
+ * (kv_rank + rot_dim)]) whose first kv_rank columns per head the caller fills with W_uk^T q_plain */
+int tha_hyb_latent_split_q(void* stream, int dtype, const tha_latent_t* a, int n_rows, const float* qfull, const float* cos_t,
+                           const float* sin_t, int rot_dims, void* q_plain, float* q_abs);
+/* out (dtype-typed [n_rows, heads * E]) = o_raw * gate_act(gate), with do_norm: o_raw divided by its rms per head and
+ * weighted by norm ([E], or [heads * E] with norm_per_head) first */
+int tha_hyb_head_gate(void* stream, int dtype, void* out, const float* o_raw, int n_rows, int heads, int E, int do_norm,
+                      float eps, const float* norm, int norm_per_head, const float* gate, long long ldg, int gate_act);
+/* gated linear attention over the rows of every sequence in order: z_raw [n_rows, heads * dim] (W_a2 a1, before the bias)
+ * is replaced by the decays; the read-out goes to o_raw (fp32 [n_rows, heads * vdim]) and, normed and gated, to out */
+int tha_hyb_gla_scan(void* stream, int dtype, const tha_gla_t* g, const tha_rows_t* rows, const tha_state_store_t* st,
+                     const float* proj, long long ldp, float* z_raw, float* o_raw, void* out);
 /* router: expert ids and weights [n_rows, top]; rows sorted by expert: group_off (2 * (experts + 1) ints: the offsets,
  * then scratch), sorted_row [n_rows * top] and the position of (row, j) in that order, inv [n_rows * top] */
 int tha_hyb_moe_route(void* stream, const tha_moe_t* e, const float* proj, long long ldp, int n_rows, int* expert_id,
@@ -204,6 +322,9 @@ int tha_hyb_moe_route(void* stream, const tha_moe_t* e, const float* proj, long 
 /* y = g * sigmoid(alpha g) * (u + 1) with the clamps; gu [n, ldg] holds gate at col_g and up at col_u; y dtype-typed [n, ff] */
 int tha_hyb_glu_clamped(void* stream, int dtype, void* y, const float* gu, long long ldg, int col_g, int col_u, int n,
                         int ff, float limit, float alpha);
+/* the same for any THA_ACT_* (ungated activations read col_u only) */
+int tha_hyb_ff_act(void* stream, int dtype, int act, void* y, const float* gu, long long ldg, int col_g, int col_u, int n,
+                   int ff, float limit, float alpha);
 
 #ifdef __cplusplus
 }
