@@ -8,6 +8,7 @@ import re
 import numpy as np
 import pytest
 
+import numizen_oracle as N
 import timerax_oracle as O
 from pkgload import load_pkg
 
@@ -39,7 +40,7 @@ def test_registry_names_what_it_knows(tmp_path):
     (tmp_path / "config.json").write_text(json.dumps({"architecture": "Nope"}))
     with pytest.raises(serving.ServingError) as e:
         serving.ServingEngine(str(tmp_path), "float32", 64, 1)
-    assert "Nope" in str(e.value) and "Timerax" in str(e.value) and "llama2" in str(e.value)
+    assert "Nope" in str(e.value) and "Timerax" in str(e.value) and "llama2" in str(e.value) and "Numizen" in str(e.value)
 
 
 @built
@@ -111,3 +112,90 @@ def test_plain_attention_sees_its_own_block_only():
     v2[3] += 1.0                                                                                     # the last of block 0
     o2 = O.chunked_attention(q, k, v2, 0.5, 4)
     assert np.allclose(o2[4:], o[4:]) and not np.allclose(o2[3], o[3])
+
+
+# ---- Numizen: config errors by name, and the plain statement's self-checks -------------------------------------------
+def _numizen_cfg(layers, **extra):
+    c = {"architecture": "Numizen", "vocab": 40, "width": 16, "norm": {"eps": 1e-5}, "max_positions": 64, "layers": layers}
+    c.update(extra)
+    return c
+
+
+@built
+def test_numizen_configs_are_refused_by_name(tmp_path):
+    serving = load_pkg("serving")
+    gla = {"type": "gla", "mixer": {"heads": 1, "dim": 4, "vdim": 4, "tau": 2.0}, "mlp": None}
+    for cfg, word in [(_numizen_cfg([{"type": "helix", "mixer": {}, "mlp": None}]), "helix"),
+                      (_numizen_cfg([gla], loop={"start": 0, "stop": 3, "times": 2}), "loop"),
+                      (_numizen_cfg([dict(gla, mlp={"kind": "sparse"})]), "sparse"),
+                      (_numizen_cfg([{"type": "gla", "mixer": {"heads": 1, "dim": 4, "vdim": 4}, "mlp": None}]), "tau")]:
+        (tmp_path / "config.json").write_text(json.dumps(cfg))
+        with pytest.raises(serving.ServingError) as e:
+            serving.ServingEngine(str(tmp_path), "float32", 64, 1)
+        assert word in str(e.value), (word, str(e.value))
+
+
+def _small_numizen():
+    lat = {"type": "latent_attention", "mlp": {"kind": "dense", "ff": 12},
+           "mixer": {"heads": 2, "dim": 4, "rot_dim": 4, "vdim": 6, "q_rank": 8, "kv_rank": 10, "scale": 0.4, "rot": {"base": 100.0, "dims": 2}}}
+    gla = {"type": "gla", "mixer": {"heads": 2, "dim": 6, "vdim": 4, "tau": 4.0},
+           "mlp": {"kind": "moe", "expert": {"ff": 8}, "shared": {"ff": 6}, "router": {"experts": 6, "top": 2, "groups": {"count": 3, "keep": 2}}}}
+    return _numizen_cfg([lat, gla], loop={"start": 0, "stop": 2, "times": 2})
+
+
+def test_plain_numizen_decoding_equals_the_whole_prompt():
+    cfg = _small_numizen()
+    W = N.random_weights(cfg, 3, gla_rank=3)
+    toks = np.random.default_rng(0).integers(0, 40, 17).tolist()
+    taps = []
+    whole = N.forward(cfg, W, toks, taps)
+    assert len(taps) == 4 and N.layer_runs(cfg) == [0, 1, 0, 1]
+    st = N.Stepper(cfg, W)
+    parts = np.concatenate([st.feed(toks[:5]), st.feed(toks[5:6]), st.feed(toks[6:])], 0)
+    assert np.allclose(parts, whole, atol=1e-9)
+    assert np.allclose(N.Stepper(cfg, W).feed(toks[:1]), whole[:1], atol=1e-12)
+
+
+def test_plain_gated_linear_attention_first_token_and_decay():
+    cfg = _small_numizen()
+    W = N.random_weights(cfg, 4, gla_rank=3)
+    m = cfg["layers"][1]["mixer"]
+    h = np.random.default_rng(1).standard_normal((3, 16))
+    # one token from the zero state: o = v (k . q) / sqrt(dim) per head, then norm, gate, projection
+    p = "l1.mix."
+    q = (h[:1] @ W[p + "q"].T).reshape(2, 6) / np.sqrt(6.0)
+    k = (h[:1] @ W[p + "k"].T).reshape(2, 6)
+    v = (h[:1] @ W[p + "v"].T).reshape(2, 4)
+    o = v * (q * k).sum(-1, keepdims=True)
+    o = N.rms_unit(o, 1e-5) * W[p + "norm"]
+    g = h[:1] @ W[p + "g"].T
+    want = (o.reshape(1, 8) * (g * N.sigmoid(g))) @ W[p + "o"].T
+    assert np.allclose(N.gla_mixer(h[:1], m, W, p, 1e-5), want, atol=1e-12)
+    # a closed gate forgets: with a very negative bias the second token sees its own write only
+    W2 = dict(W)
+    W2[p + "a2.b"] = np.full_like(W[p + "a2.b"], -200.0)
+    both = N.gla_mixer(h[:2], m, W2, p, 1e-5)
+    assert np.allclose(both[1:], N.gla_mixer(h[1:2], m, W2, p, 1e-5), atol=1e-9)
+
+
+def test_plain_router_groups_and_weights():
+    f = {"router": {"experts": 6, "top": 2, "groups": {"count": 3, "keep": 1}}}
+    W = {"r.router": np.eye(6), "r.correction": np.array([0.0, 0.0, 0.0, 0.0, 5.0, -5.0])}
+    h = np.zeros((1, 6))
+    h[0, 0] = 3.0                                     # expert 0 has by far the largest score, but group 2 wins by its correction
+    picked, w = N.route(h, f, W, "r.")
+    assert sorted(picked[0].tolist()) == [4, 5]      # both of the kept group, although expert 5's choice score is negative
+    assert np.allclose(w.sum(), 1.0) and np.allclose(w[0, 0], w[0, 1])   # equal scores s: the correction is not in the weights
+    f["router"]["groups"]["keep"] = 3
+    picked, _ = N.route(h, f, W, "r.")
+    assert sorted(picked[0].tolist()) == [0, 4]
+
+
+def test_plain_rotation_pairs_neighbours():
+    x = np.arange(8.0).reshape(1, 8)
+    r = N.rotate(x, [0], 4, 10.0)
+    assert np.allclose(r, x)                          # position 0: unchanged
+    r = N.rotate(x, [1], 4, 10.0)
+    a0, a1 = 1.0, 10.0 ** -0.5                        # f_i = base^(-2i/dims)
+    assert np.allclose(r[0, 0], 0 * np.cos(a0) - 1 * np.sin(a0)) and np.allclose(r[0, 1], 1 * np.cos(a0) + 0 * np.sin(a0))
+    assert np.allclose(r[0, 2], 2 * np.cos(a1) - 3 * np.sin(a1)) and np.allclose(r[0, 4:], x[0, 4:])
