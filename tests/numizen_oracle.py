@@ -67,9 +67,10 @@ def latent_project(h, pos, m, W, p, eps):
     kv = h @ W[p + "dkv"].T
     c = rms_unit(kv[:, :K], eps) * W[p + "dkv.norm"]
     kr = kv[:, K:]
-    dims, base = m["rot"]["dims"], m["rot"]["base"]
-    q = np.concatenate([q[..., :D], rotate(q[..., D:], pos, dims, base)], axis=-1)
-    kr = rotate(kr, pos, dims, base)
+    if m.get("rot"):                                           # no rotary setting: nothing is rotated
+        dims, base = m["rot"]["dims"], m["rot"]["base"]
+        q = np.concatenate([q[..., :D], rotate(q[..., D:], pos, dims, base)], axis=-1)
+        kr = rotate(kr, pos, dims, base)
     return q, c, kr, h @ W[p + "g"].T
 
 

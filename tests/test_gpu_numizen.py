@@ -322,14 +322,22 @@ def test_pool_exhaustion_and_the_end_of_the_position_table_are_errors_not_faults
 
 # ---- sharp attention: far keys, borders of the block table --------------------------------------------------------------
 def sharp_model(tmp, vocab=1024, rot_dim=4):
-    """keys equal queries in the plain part (the query latent is the key latent, the query expansion is the key
-    expansion), a large score scale, small position vectors: a query finds the earlier occurrence of its own token"""
+    """The query latent reads the upper half of the layer's input, the key/value latent the lower half, through the same
+    matrix; the query expansion is the key expansion; the score scale is large and the position vectors are small.  The
+    upper half of the embedding of the QUERY probe is the lower half of the embedding of the KEY probe, so the query probe
+    puts nearly all its weight on the key probe wherever that is -- a different token with a different value, so losing
+    that key (or seeing another in its place) moves the output at the query a lot."""
     cfg = model([latent(None, heads=2, dim=16, rot_dim=rot_dim, vdim=16, q_rank=24, kv_rank=24, scale=2.5),
                  latent(moe(), heads=2)], width=64, vocab=vocab)
 
     def tweak(w):
         w["pos"][...] *= 0.02
-        w["l0.mix.dq"][...] = w["l0.mix.dkv"][:24]
+        w["embed"][vocab - 2, 32:] = w["embed"][vocab - 1, :32]
+        for n in ("l0.norm1", "l0.norm1.b"):
+            w[n][32:] = w[n][:32]
+        w["l0.mix.dkv"][:24, 32:] = 0.0
+        w["l0.mix.dq"][:, :32] = 0.0
+        w["l0.mix.dq"][:, 32:] = w["l0.mix.dkv"][:24, :32]
         w["l0.mix.dq.norm"][...] = w["l0.mix.dkv.norm"]
         uq = w["l0.mix.uq"].reshape(2, 16 + rot_dim, 24)
         uq[:, :16] = w["l0.mix.uk"].reshape(2, 16, 24)
@@ -339,20 +347,25 @@ def sharp_model(tmp, vocab=1024, rot_dim=4):
 
 
 def distinct_tokens(n, vocab, seed):
-    return np.random.default_rng(seed).permutation(vocab - 1)[:n].tolist()   # token vocab-1 is kept for the probe
+    return np.random.default_rng(seed).permutation(vocab - 2)[:n].tolist()   # the last two tokens are the probes
+
+
+def with_probes(b, n, key_pos, query_pos, seed):
+    """distinct tokens with the key probe and the query probe in place; and the same without the key probe"""
+    toks = distinct_tokens(n + 1, b.cfg["vocab"], seed)
+    spare = toks.pop()
+    toks[key_pos], toks[query_pos] = b.cfg["vocab"] - 1, b.cfg["vocab"] - 2
+    other = list(toks)
+    other[key_pos] = spare
+    return toks, other
 
 
 @pytest.mark.parametrize("key_pos,query_pos", [(0, 1), (0, 149), (63, 64), (64, 65), (63, 127), (64, 128), (127, 128), (1, 63)])
 def test_keys_at_the_borders_of_the_block_table(tmp_path, key_pos, query_pos):
     b = sharp_model(tmp_path)
-    probe = b.cfg["vocab"] - 1
-    toks = distinct_tokens(150, b.cfg["vocab"], key_pos * 7 + query_pos)
-    toks[key_pos] = probe
-    toks[query_pos] = probe
+    toks, other = with_probes(b, 150, key_pos, query_pos, key_pos * 7 + query_pos)
     z, _ = b.ref(toks)
-    other = list(toks)
-    other[key_pos] = distinct_tokens(151, b.cfg["vocab"], 1)[150]
-    assert rel_err(b.ref(other)[0][query_pos], z[query_pos]) > 0.02      # the probe's key does carry the weight
+    assert rel_err(b.ref(other)[0][query_pos], z[query_pos]) > 0.1       # the probe's key does carry the weight
     for cuts in ([150], [query_pos, 1], [key_pos, 2, 1], [key_pos + 1, 1]):
         cuts = [c for c in cuts if c > 0] or [1]
         got = feed(b.engine(), "a", toks, cuts)
@@ -363,15 +376,10 @@ def test_keys_at_the_borders_of_the_block_table(tmp_path, key_pos, query_pos):
 @pytest.mark.parametrize("dtype,decoded", [("float32", False), ("float32", True), ("bfloat16", True)])
 def test_one_far_key_among_hundreds(tmp_path, dtype, decoded):
     b = sharp_model(tmp_path)
-    probe = b.cfg["vocab"] - 1
-    toks = distinct_tokens(700, b.cfg["vocab"], 5)
-    toks[3] = probe
-    toks[690] = probe
+    toks, other = with_probes(b, 700, 3, 690, 5)
     z, _ = b.ref(toks)
-    other = list(toks)
-    other[3] = distinct_tokens(701, b.cfg["vocab"], 1)[700]
     moved = rel_err(b.ref(other)[0][690], z[690])
-    assert moved > 0.02
+    assert moved > 0.1
     got = feed(b.engine(dtype), "a", toks, [670, 1] if decoded else [300, 400])
     if dtype == "float32":
         assert rel_err(got[690], z[690]) < 10 * F32_TOL
