@@ -56,7 +56,7 @@ def parse_args():
                     "over the GPUs, all-reduce fused into its consumer over NVLink peer memory (strong scaling)")
     ap.add_argument("--pos0", type=int, default=0, help="profiling aid: slots start at this position over a zero-filled KV cache "
                     "(same bytes and time per step as a real context of that length); the default 0 is the benchmark")
-    ap.add_argument("--design", default="", choices=["", "timerax"], help="instead of the default workload: prompt and decode throughput of "
+    ap.add_argument("--design", default="", choices=["", "timerax", "numizen"], help="instead of the default workload: prompt and decode throughput of "
                     "this layer-program design at a few realistic layer sizes (random weights), beside the llama2 bf16 path at equal size")
     ap.add_argument("--design-sizes", default="w1024,w2048")
     ap.add_argument("--design-prompt", type=int, default=4096)
@@ -772,7 +772,7 @@ def main():
         from pkgload import load_pkg
         bd = load_pkg("bench_designs")
         res = bd.run(load_pkg, args.design_sizes.split(","), prompt_len=args.design_prompt, batch=args.design_batch, steps=max(4, min(args.steps, 32)),
-                     warmup=max(3, min(args.warmup, 8)), kernels=args.kernels, llama=not (args.kernels or args.design_only))
+                     warmup=max(3, min(args.warmup, 8)), kernels=args.kernels, llama=not (args.kernels or args.design_only), design=args.design)
         print(json.dumps({"design": args.design, "dtype": "bf16", "data": "synthetic (random weights)", "n_gpus": 1,
                           "timing": "wall clock around the engine's step call (rows up, wanted logits back, stream synchronised), median",
                           "sizes": res}))

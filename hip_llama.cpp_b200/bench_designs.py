@@ -1,4 +1,6 @@
-"""Throughput of a layer-program design beside the llama2 bf16 path at equal size (bench.py --design timerax).
+"""Throughput of a layer-program design beside the llama2 bf16 path at equal size (bench.py --design timerax), or of
+Numizen beside Timerax -- the closest design the framework has: attention + a recurrent mixer + a mixture of experts --
+and llama2 at equal size (bench.py --design numizen).
 
 Random weights at sizes that resemble a real model's layers; a few layers only, so that building the folder stays
 short.  For every size: prompt ingestion (one prompt in one step) and batched decoding (one token per live request per
@@ -38,6 +40,30 @@ def timerax_config(s: dict) -> dict:
           "mlp": mlp}
     layers = [dl if i % 4 == 2 else par for i in range(s["layers"])]
     return {"architecture": "Timerax", "layers": layers, "logit_softcap": 30.0, "norm": {"eps": 1e-5}, "vocab": s["vocab"], "width": s["width"]}
+
+
+# Numizen at the same widths, expert counts and vocabulary.  Layer 0 has a dense feed-forward as wide as the experts a
+# token uses, the others the mixture; layer 2 is the gated linear attention.  "w1024" keeps the cached row (latent +
+# rotated part) at 128 channels; "w2048" has the full-size latent of 512 + 64.
+NUMIZEN = {
+    "w1024": dict(heads=8, dim=64, rot_dim=32, vdim=64, q_rank=384, kv_rank=96, gheads=4, gdim=128, gvdim=256, groups=(4, 2)),
+    "w2048": dict(heads=16, dim=128, rot_dim=64, vdim=128, q_rank=768, kv_rank=512, gheads=8, gdim=128, gvdim=256, groups=(4, 2)),
+}
+
+
+def numizen_config(s: dict, n: dict, max_positions: int = 8192) -> dict:
+    lat = {"heads": n["heads"], "dim": n["dim"], "rot_dim": n["rot_dim"], "vdim": n["vdim"], "q_rank": n["q_rank"], "kv_rank": n["kv_rank"],
+           "scale": (n["dim"] + n["rot_dim"]) ** -0.5, "rot": {"base": 500000.0, "dims": n["rot_dim"]}}
+    gl = {"heads": n["gheads"], "dim": n["gdim"], "vdim": n["gvdim"], "tau": 16.0}
+    moe = {"kind": "moe", "expert": {"ff": s["ff"]}, "shared": {"ff": s["sff"]},
+           "router": {"experts": s["experts"], "top": s["top"], "groups": {"count": n["groups"][0], "keep": n["groups"][1]}}}
+    dense = {"kind": "dense", "ff": s["top"] * s["ff"] + s["sff"]}
+    layers = []
+    for i in range(s["layers"]):
+        mlp = dense if i == 0 else moe
+        layers.append({"type": "gla", "mixer": gl, "mlp": mlp} if i % 4 == 2 else {"type": "latent_attention", "mixer": lat, "mlp": mlp})
+    return {"architecture": "Numizen", "layers": layers, "norm": {"eps": 1e-5}, "vocab": s["vocab"], "width": s["width"],
+            "max_positions": max_positions}
 
 
 def _time_timerax(serving, folder, prompt_len, batch, ctx, steps, warmup, kernels):
@@ -146,6 +172,10 @@ def _time_llama(engine_mod, checkpoint_mod, s, prompt_len, batch, ctx, steps, wa
     return out
 
 
+def _time_folder(serving, folder, *a):
+    return _time_timerax(serving, folder, *a)   # the workloads are the same for every layer-program design
+
+
 def timerax_weight_bytes(cfg: dict, shapes: dict) -> dict:
     total = sum(int(np.prod(sh)) for sh in shapes.values()) * 2
     active = 0
@@ -159,19 +189,32 @@ def timerax_weight_bytes(cfg: dict, shapes: dict) -> dict:
     return {"total": total, "per_token": int(active)}
 
 
-def run(load_pkg, sizes, prompt_len=4096, batch=64, ctx=512, steps=16, warmup=3, kernels=False, llama=True):
+def run(load_pkg, sizes, prompt_len=4096, batch=64, ctx=512, steps=16, warmup=3, kernels=False, llama=True, design="timerax"):
     serving = load_pkg("serving")
     engine_mod = load_pkg("engine")
     checkpoint_mod = load_pkg("checkpoint")
     results = {}
     for name in sizes:
         s = SIZES[name]
+        r = {}
+        if design == "numizen":
+            ncfg = numizen_config(s, NUMIZEN[name], max_positions=max(prompt_len, ctx + steps + warmup) + 64)
+            tmp = tempfile.mkdtemp(prefix="design_bench_")
+            try:
+                serving.save_model_folder(tmp, ncfg, serving.random_numizen_tensors(ncfg, 0))
+                r["numizen"] = _time_folder(serving, tmp, prompt_len, batch, ctx, steps, warmup, kernels)
+                r["numizen"]["weights_bytes"] = timerax_weight_bytes(ncfg, serving.numizen_tensor_shapes(ncfg))
+            finally:
+                shutil.rmtree(tmp, ignore_errors=True)
+            if kernels:
+                results[name] = r
+                continue
         cfg = timerax_config(s)
         shapes = serving.timerax_tensor_shapes(cfg)
         tmp = tempfile.mkdtemp(prefix="design_bench_")
         try:
             serving.save_model_folder(tmp, cfg, serving.random_timerax_tensors(cfg, 0))
-            r = {"timerax": _time_timerax(serving, tmp, prompt_len, batch, ctx, steps, warmup, kernels)}
+            r["timerax"] = _time_timerax(serving, tmp, prompt_len, batch, ctx, steps, warmup, kernels)
             r["timerax"]["weights_bytes"] = timerax_weight_bytes(cfg, shapes)
         finally:
             shutil.rmtree(tmp, ignore_errors=True)

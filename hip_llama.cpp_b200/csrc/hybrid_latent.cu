@@ -75,6 +75,232 @@ __global__ void hyb_latent_split_q_kernel(tha_latent_t a, int n_rows, const floa
   }
 }
 
+
+// ------------------------------------------------------------------------------------------------------------------
+// Tensor-core attention for WIDE key rows whose values are their first vdim channels (the absorbed form of latent
+// attention: 512 + 64 channels at full size).  Neither a query row nor a row of the output fits a warp's registers at
+// that width, so a block shares them: 16 * MT (position, query head) pairs, 4 * MT warps; warp (mi, ei) owns row tile
+// mi (16 pairs) and slice ei of four.  Per tile of 32 keys (aligned to absolute multiples of 32, like the other forms):
+//   1. the tile's key rows go to shared memory once, as bf16 -- they are also the values;
+//   2. warp (mi, ei): scores of its 16 pairs against keys 8 ei .. 8 ei + 7 (mma.sync m16n8k16, queries and keys from
+//      shared memory), written to shared memory in fp32;
+//   3. a warp takes 4 pairs (lane = key): scale, mask, running maximum and sum in fp32, weights rounded to bf16 (the sums
+//      add the rounded weights), the rescale factor of each pair;
+//   4. warp (mi, ei): rescales its accumulators [16 pairs, vdim / 4 channels] and adds weights x values; the value
+//      fragments come out of the row-major key tile through ldmatrix.trans.
+// Three block barriers per tile.  Splits along the keys and their merge as in the other forms.
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int WK_KEYS = 32, WK_MAX_SLICE = 128;   // channels of the output per warp: vdim <= 512
+
+__device__ __forceinline__ void mma_bf16_m16n8k16(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+template <int MT>
+__global__ void __launch_bounds__(128 * MT) hyb_attn_wide_kernel(tha_attn_t a, tha_rows_t rows, tha_kv_t kv, const float* __restrict__ q,
+                                                                 __nv_bfloat16* __restrict__ out, int AG, int AP, int splits,
+                                                                 float* __restrict__ partial) {
+  constexpr int PAIRS = 16 * MT, NW = 4 * MT;
+  extern __shared__ __align__(16) unsigned char smraw[];
+  const int D = a.dim, E = a.vdim, gsize = a.heads / a.kv_heads, ES = E / 4;
+  const int DS = D + 8;                                   // padded rows: conflict-free fragment and ldmatrix reads
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smraw);          // [PAIRS][DS]
+  __nv_bfloat16* Ks = Qs + (size_t)PAIRS * DS;                             // [32][DS]
+  __nv_bfloat16* Pb = Ks + (size_t)WK_KEYS * DS;                           // [PAIRS][40] weights
+  float* Sf = reinterpret_cast<float*>(Pb + PAIRS * 40);                   // [PAIRS][33] scores
+  float* corr_s = Sf + PAIRS * 33;                                         // [PAIRS] rescale factors, then 1 / sum
+  float* m_s = corr_s + PAIRS;                                             // [PAIRS] running maxima at the end
+  int seq = -1, r0 = 0, r_end = 0;
+  {
+    int tile = blockIdx.x / splits;
+    for (int s = 0; s < rows.n_seqs; s++) {
+      const int lo = rows.seq_first[s], hi = rows.seq_first[s + 1];
+      const int nt = (hi - lo + AP - 1) / AP;
+      if (tile < nt) { seq = s; r0 = lo + tile * AP; r_end = min(hi, r0 + AP); break; }
+      tile -= nt;
+    }
+    if (seq < 0) return;
+  }
+  const int g = blockIdx.y, part = blockIdx.z;
+  const int slot = rows.seq_slot[seq];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int mi = warp >> 2, ei = warp & 3;
+  const int p_first = rows.pos[r0], p_last = p_first + (r_end - r0) - 1;
+  const int lr = lane >> 2, lc = (lane & 3) * 2;
+  // pair pr of the block: position r0 + pr / AG, head g * gsize + part * AG + pr % AG
+  auto pair_row = [&](int pr) { return r0 + pr / AG; };
+  auto pair_head = [&](int pr) { return g * gsize + part * AG + pr % AG; };
+  auto pair_ok = [&](int pr) { return pr / AG < AP && r0 + pr / AG < r_end && part * AG + pr % AG < gsize; };
+  // queries -> shared memory (bf16), rows of absent pairs zero
+  for (int pr = warp; pr < PAIRS; pr += NW) {
+    const bool ok = pair_ok(pr);
+    const float* qr = q + (size_t)(ok ? pair_row(pr) : 0) * a.heads * D + (size_t)(ok ? pair_head(pr) : 0) * D;
+    for (int d = lane; d < D; d += 32) Qs[(size_t)pr * DS + d] = __float2bfloat16_rn(ok ? qr[d] : 0.f);
+  }
+  // the softmax state of this warp's 4 pairs (identical in every lane)
+  float m_run[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY}, l_run[4] = {0.f, 0.f, 0.f, 0.f};
+  int s_pos[4];
+  bool s_ok[4];
+#pragma unroll
+  for (int rr = 0; rr < 4; rr++) {
+    const int pr = warp * 4 + rr;
+    s_ok[rr] = pair_ok(pr);
+    s_pos[rr] = p_first + pr / AG;
+  }
+  float oacc[WK_MAX_SLICE / 8][4];
+#pragma unroll
+  for (int n = 0; n < WK_MAX_SLICE / 8; n++)
+#pragma unroll
+    for (int v = 0; v < 4; v++) oacc[n][v] = 0.f;
+  int kt_begin = 0, kt_last = p_last;
+  if (splits > 1) {
+    const int n_kt = p_last / WK_KEYS + 1, per = (n_kt + splits - 1) / splits, sp = blockIdx.x % splits;
+    kt_last = min(p_last, (sp + 1) * per * WK_KEYS - 1);
+    kt_begin = sp * per * WK_KEYS;
+  }
+  const unsigned ks_base = (unsigned)__cvta_generic_to_shared(Ks);
+  for (int kt = kt_begin; kt <= kt_last; kt += WK_KEYS) {
+    __syncthreads();   // the previous tile's weights and values have been used (first pass: the queries are in place)
+    // 1. the tile's key rows; keys past the last position of the block are zero
+    for (int j = warp; j < WK_KEYS; j += NW) {
+      const int t = kt + j;
+      const bool live = t <= p_last;
+      const float* src = kv.k_pool + (live ? hyb_kv_row(kv, slot, t, a.cache_layer) : 0) + (size_t)g * D;
+      for (int d0 = 0; d0 < D; d0 += 128) {
+        float buf[4];
+#pragma unroll
+        for (int c = 0; c < 4; c++) { const int d = d0 + lane + 32 * c; buf[c] = (live && d < D) ? __ldg(src + d) : 0.f; }
+#pragma unroll
+        for (int c = 0; c < 4; c++) { const int d = d0 + lane + 32 * c; if (d < D) Ks[(size_t)j * DS + d] = __float2bfloat16_rn(buf[c]); }
+      }
+    }
+    __syncthreads();
+    // 2. scores of row tile mi against keys 8 ei .. 8 ei + 7
+    {
+      float sacc[4] = {0.f, 0.f, 0.f, 0.f};
+      const __nv_bfloat16* qa = Qs + (size_t)(mi * 16 + lr) * DS + lc;
+      const __nv_bfloat16* kb = Ks + (size_t)(ei * 8 + lr) * DS + lc;
+      for (int k0 = 0; k0 < D; k0 += 16) {
+        uint32_t af[4], bf[2];
+        af[0] = *reinterpret_cast<const uint32_t*>(qa + k0);
+        af[1] = *reinterpret_cast<const uint32_t*>(qa + 8 * DS + k0);
+        af[2] = *reinterpret_cast<const uint32_t*>(qa + k0 + 8);
+        af[3] = *reinterpret_cast<const uint32_t*>(qa + 8 * DS + k0 + 8);
+        bf[0] = *reinterpret_cast<const uint32_t*>(kb + k0);
+        bf[1] = *reinterpret_cast<const uint32_t*>(kb + k0 + 8);
+        mma_bf16_m16n8k16(sacc, af, bf);
+      }
+      float* sr = Sf + (mi * 16 + lr) * 33 + ei * 8 + lc;
+      sr[0] = sacc[0]; sr[1] = sacc[1];
+      sr[8 * 33] = sacc[2]; sr[8 * 33 + 1] = sacc[3];
+    }
+    __syncthreads();
+    // 3. online softmax of this warp's 4 pairs, lane = key
+#pragma unroll
+    for (int rr = 0; rr < 4; rr++) {
+      const int pr = warp * 4 + rr, t = kt + lane;
+      const bool vis = s_ok[rr] && t <= s_pos[rr];
+      const float sv = vis ? Sf[pr * 33 + lane] * a.scale : -INFINITY;
+      const float m_new = fmaxf(m_run[rr], warp_max(sv));
+      float p = 0.f, corr = 1.f;
+      if (m_new > -INFINITY) {
+        p = vis ? expf(sv - m_new) : 0.f;
+        corr = expf(m_run[rr] - m_new);      // 0 when nothing was seen before
+      }
+      const __nv_bfloat16 pb = __float2bfloat16_rn(p);
+      l_run[rr] = l_run[rr] * corr + warp_sum(__bfloat162float(pb));
+      m_run[rr] = m_new;
+      Pb[pr * 40 + lane] = pb;
+      if (lane == 0) corr_s[pr] = corr;
+    }
+    __syncthreads();
+    // 4. accumulators of row tile mi, channels ei * ES ..: rescale, then weights x values
+    {
+      const float ca = corr_s[mi * 16 + lr], cb = corr_s[mi * 16 + lr + 8];
+      uint32_t pf[2][4];
+      const __nv_bfloat16* pa = Pb + (mi * 16 + lr) * 40 + lc;
+#pragma unroll
+      for (int t2 = 0; t2 < 2; t2++) {
+        pf[t2][0] = *reinterpret_cast<const uint32_t*>(pa + 16 * t2);
+        pf[t2][1] = *reinterpret_cast<const uint32_t*>(pa + 8 * 40 + 16 * t2);
+        pf[t2][2] = *reinterpret_cast<const uint32_t*>(pa + 16 * t2 + 8);
+        pf[t2][3] = *reinterpret_cast<const uint32_t*>(pa + 8 * 40 + 16 * t2 + 8);
+      }
+#pragma unroll
+      for (int n = 0; n < WK_MAX_SLICE / 8; n++) {
+        if (8 * n < ES) {
+          oacc[n][0] *= ca; oacc[n][1] *= ca; oacc[n][2] *= cb; oacc[n][3] *= cb;
+#pragma unroll
+          for (int t2 = 0; t2 < 2; t2++) {
+            // values [key][channel] row-major: lanes 0..15 name the rows of keys 16 t2 + (lane & 15); transposed on the way
+            uint32_t vf[2];
+            const unsigned addr = ks_base + (unsigned)(((size_t)(16 * t2 + (lane & 15)) * DS + ei * ES + 8 * n) * sizeof(__nv_bfloat16));
+            asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];" : "=r"(vf[0]), "=r"(vf[1]) : "r"(addr));
+            mma_bf16_m16n8k16(oacc[n], pf[t2], vf);
+          }
+        }
+      }
+    }
+  }
+  // the sums and maxima of the pairs, for the warps that hold their accumulators
+  __syncthreads();
+  if (lane == 0) {
+#pragma unroll
+    for (int rr = 0; rr < 4; rr++) { corr_s[warp * 4 + rr] = l_run[rr]; m_s[warp * 4 + rr] = m_run[rr]; }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int x = 0; x < 2; x++) {
+    const int pr = mi * 16 + lr + 8 * x;
+    if (!pair_ok(pr)) continue;
+    const int row = pair_row(pr), head = pair_head(pr);
+    const float l = corr_s[pr];
+    if (splits > 1) {
+      float* dst = partial + (((size_t)(blockIdx.x % splits) * rows.n_rows + row) * a.heads + head) * (E + 2);
+#pragma unroll
+      for (int n = 0; n < WK_MAX_SLICE / 8; n++)
+        if (8 * n < ES) { dst[ei * ES + 8 * n + lc] = oacc[n][2 * x]; dst[ei * ES + 8 * n + lc + 1] = oacc[n][2 * x + 1]; }
+      if (ei == 0 && (lane & 3) == 0) { dst[E] = m_s[pr]; dst[E + 1] = l; }
+      continue;
+    }
+    const float inv = 1.0f / l;
+    __nv_bfloat16* dst = out + (size_t)row * a.heads * E + (size_t)head * E + ei * ES;
+#pragma unroll
+    for (int n = 0; n < WK_MAX_SLICE / 8; n++)
+      if (8 * n < ES) *reinterpret_cast<__nv_bfloat162*>(dst + 8 * n + lc) = __floats2bfloat162_rn(oacc[n][2 * x] * inv, oacc[n][2 * x + 1] * inv);
+  }
+}
+
+static size_t wide_smem(const tha_attn_t* a, int pairs) {
+  return sizeof(__nv_bfloat16) * ((size_t)(pairs + WK_KEYS) * (a->dim + 8) + (size_t)pairs * 40) + sizeof(float) * ((size_t)pairs * 33 + 2 * pairs);
+}
+
+// one key/value head, key rows a multiple of 16 wide, values inside them, four slices of at most 128 channels that are multiples of 8, no
+// block-of-positions mask, and the larger block must fit shared memory
+bool hyb_attn_wide_ok(const tha_attn_t* a) {
+  return a->values_in_keys && a->kv_heads == 1 && a->chunk == 0 && a->dim % 16 == 0 && a->vdim % 32 == 0 && a->vdim <= 4 * WK_MAX_SLICE && a->vdim <= a->dim &&
+         (a->heads * a->vdim) % 2 == 0 && wide_smem(a, 64) <= 200 * 1024;
+}
+// 64 pairs per block when the step has prompt portions that fill them, else 16
+int hyb_attn_wide_pairs(const tha_attn_t* a, const tha_rows_t* rows) {
+  const long long per_seq = (long long)rows->max_seq_rows * (a->heads / a->kv_heads);
+  return per_seq >= 64 ? 64 : 16;
+}
+int hyb_attn_wide_launch(cudaStream_t s, const tha_attn_t* a, const tha_rows_t* rows, const tha_kv_t* kv, const float* q, __nv_bfloat16* out,
+                         dim3 grid, int pairs, int AG, int AP, int splits, float* partial) {
+  const size_t smem = wide_smem(a, pairs);
+  if (pairs == 64) {
+    THA_CUDA_OK(cudaFuncSetAttribute(hyb_attn_wide_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    THA_CUDA_OK(launch(hyb_attn_wide_kernel<4>, grid, dim3(512), smem, s, false, *a, *rows, *kv, q, out, AG, AP, splits, partial));
+  } else {
+    THA_CUDA_OK(cudaFuncSetAttribute(hyb_attn_wide_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    THA_CUDA_OK(launch(hyb_attn_wide_kernel<1>, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, out, AG, AP, splits, partial));
+  }
+  return THA_STATUS_SUCCESS;
+}
+
 }  // namespace tha
 
 using namespace tha;

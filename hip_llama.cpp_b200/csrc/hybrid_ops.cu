@@ -296,9 +296,9 @@ __global__ void hyb_attn_prepare_kernel(tha_attn_t a, tha_rows_t rows, tha_kv_t 
 // Per tile: scores (warp = 4 pairs, lane = key), masked to the query's visible range [start of its block of `chunk`
 // positions, own position], online softmax per pair, then P.V with lanes over value channels.
 // ------------------------------------------------------------------------------------------------------------------
-constexpr int ATT_PAIRS = 16, ATT_KEYS = 32, ATT_MAX_VC = 8;   // value channels per lane: vdim <= 256
+constexpr int ATT_PAIRS = 16, ATT_KEYS = 32, ATT_MAX_VC = 16;   // value channels per lane (template VC: 8 up to vdim 256, else 16)
 
-template <typename T>
+template <typename T, int VC>
 __global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t rows, tha_kv_t kv, const float* __restrict__ q,
                                                        T* __restrict__ out, int AG, int AP, int splits, float* __restrict__ partial) {
   extern __shared__ __align__(16) float sm[];
@@ -333,7 +333,7 @@ __global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t 
   }
   int my_pos[4], my_first[4];
   bool my_ok[4];
-  float m_run[4], l_run[4], acc[4][ATT_MAX_VC];
+  float m_run[4], l_run[4], acc[4][VC];
 #pragma unroll
   for (int rr = 0; rr < 4; rr++) {
     const int pr = warp * 4 + rr;
@@ -343,7 +343,7 @@ __global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t 
     my_first[rr] = a.chunk > 0 ? (my_pos[rr] / a.chunk) * a.chunk : 0;
     m_run[rr] = -INFINITY; l_run[rr] = 0.f;
 #pragma unroll
-    for (int c = 0; c < ATT_MAX_VC; c++) acc[rr][c] = 0.f;
+    for (int c = 0; c < VC; c++) acc[rr][c] = 0.f;
   }
   const int key_lo = a.chunk > 0 ? (p_first / a.chunk) * a.chunk : 0;
   // with splits > 1 (few rows, long contexts) the key tiles are dealt to `splits` blocks in contiguous runs; each leaves
@@ -371,24 +371,24 @@ __global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t 
       float* dst = which ? Vs : Ks;
 #pragma unroll
       for (int j0 = 0; j0 < ATT_KEYS / 4; j0 += 4) {
-        float buf[4][ATT_MAX_VC];
+        float buf[4][VC];
 #pragma unroll
         for (int jj = 0; jj < 4; jj++) {
           const bool live = krow[j0 + jj] != (size_t)-1;
           const float* src = pool + (live ? krow[j0 + jj] : 0) + (size_t)g * width;
 #pragma unroll
-          for (int c = 0; c < ATT_MAX_VC; c++) buf[jj][c] = (live && lane + 32 * c < width) ? __ldg(src + lane + 32 * c) : 0.f;
+          for (int c = 0; c < VC; c++) buf[jj][c] = (live && lane + 32 * c < width) ? __ldg(src + lane + 32 * c) : 0.f;
         }
 #pragma unroll
         for (int jj = 0; jj < 4; jj++) {
           const int j = warp + 4 * (j0 + jj);
 #pragma unroll
-          for (int c = 0; c < ATT_MAX_VC; c++)
+          for (int c = 0; c < VC; c++)
             if (lane + 32 * c < width) dst[j * stride + lane + 32 * c] = buf[jj][c];
-          if (width > 32 * ATT_MAX_VC) {   // wider key rows than the register buffer: the rest one by one
+          if (width > 32 * VC) {   // wider key rows than the register buffer: the rest one by one
             const bool live = krow[j0 + jj] != (size_t)-1;
             const float* src = pool + (live ? krow[j0 + jj] : 0) + (size_t)g * width;
-            for (int d = lane + 32 * ATT_MAX_VC; d < width; d += 32) dst[j * stride + d] = live ? src[d] : 0.f;
+            for (int d = lane + 32 * VC; d < width; d += 32) dst[j * stride + d] = live ? src[d] : 0.f;
           }
         }
       }
@@ -432,7 +432,7 @@ __global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t 
       m_run[rr] = m_new;
       Ps[(warp * 4 + rr) * ATT_KEYS + lane] = p;
 #pragma unroll
-      for (int c = 0; c < ATT_MAX_VC; c++) acc[rr][c] *= corr;
+      for (int c = 0; c < VC; c++) acc[rr][c] *= corr;
     }
     __syncwarp();
     const float* pw = Ps + (warp * 4) * ATT_KEYS;
@@ -446,7 +446,7 @@ __global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t 
         for (int jj = 0; jj < 4; jj++) {
           const float* vrow = Vs + (4 * j4 + jj) * E;
 #pragma unroll
-          for (int c = 0; c < ATT_MAX_VC; c++) {
+          for (int c = 0; c < VC; c++) {
             const int e = lane + 32 * c;
             if (e < E) {
               const float v = vrow[e];
@@ -462,7 +462,7 @@ __global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t 
       for (int j = 0; j < ATT_KEYS; j++) {
         const float p0 = pw[j], p1 = pw[ATT_KEYS + j], p2 = pw[2 * ATT_KEYS + j], p3 = pw[3 * ATT_KEYS + j];
 #pragma unroll
-        for (int c = 0; c < ATT_MAX_VC; c++) {
+        for (int c = 0; c < VC; c++) {
           const int e = lane + 32 * c;
           if (e < E) {
             const float v = Vs[j * E + e];
@@ -483,7 +483,7 @@ __global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t 
     if (splits > 1) {
       float* dst = partial + (((size_t)(blockIdx.x % splits) * rows.n_rows + r) * a.heads + h) * (E + 2);
 #pragma unroll
-      for (int c = 0; c < ATT_MAX_VC; c++) {
+      for (int c = 0; c < VC; c++) {
         const int e = lane + 32 * c;
         if (e < E) dst[e] = acc[rr][c];
       }
@@ -492,7 +492,7 @@ __global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t 
     }
     const float inv = 1.0f / l_run[rr];
 #pragma unroll
-    for (int c = 0; c < ATT_MAX_VC; c++) {
+    for (int c = 0; c < VC; c++) {
       const int e = lane + 32 * c;
       if (e < E) hyb_store(out + (size_t)r * a.heads * E + (size_t)h * E + e, acc[rr][c] * inv);
     }
@@ -1427,6 +1427,14 @@ extern "C" int tha_hyb_attn_prepare(void* stream, const tha_attn_t* a, const tha
   return THA_STATUS_SUCCESS;
 }
 
+namespace tha {
+// hybrid_latent.cu: tensor-core attention for key rows wider than AM_MAXD whose values lie inside the keys
+bool hyb_attn_wide_ok(const tha_attn_t* a);
+int hyb_attn_wide_pairs(const tha_attn_t* a, const tha_rows_t* rows);
+int hyb_attn_wide_launch(cudaStream_t s, const tha_attn_t* a, const tha_rows_t* rows, const tha_kv_t* kv, const float* q, __nv_bfloat16* out,
+                         dim3 grid, int pairs, int AG, int AP, int splits, float* partial);
+}  // namespace tha
+
 extern "C" int tha_hyb_attn(void* stream, int dtype, const tha_attn_t* a, const tha_rows_t* rows, const tha_kv_t* kv, const float* q,
                             void* out, float* split_scratch, size_t split_scratch_floats) {
   if (rows->n_rows < 1) return THA_STATUS_SUCCESS;
@@ -1435,11 +1443,12 @@ extern "C" int tha_hyb_attn(void* stream, int dtype, const tha_attn_t* a, const 
   // bf16 with heads the tensor-core form covers: 64 pairs per block; else 16 pairs on the fp32 cores
   const bool tc = dtype == THA_DT_BF16 && hyb_tc_linear() && a->dim % 16 == 0 && a->vdim % 8 == 0 && a->dim <= AM_MAXD && a->vdim <= AM_MAXD &&
                   (a->heads * a->vdim) % 2 == 0;
-  const int pairs = tc ? AM_PAIRS : ATT_PAIRS;
+  const bool wide = !tc && dtype == THA_DT_BF16 && hyb_tc_linear() && hyb_attn_wide_ok(a);
+  const int pairs = wide ? hyb_attn_wide_pairs(a, rows) : tc ? AM_PAIRS : ATT_PAIRS;
   const int AG = gsize < pairs ? gsize : pairs, AP = pairs / AG;
   const size_t smem = tc ? sizeof(__nv_bfloat16) * ((size_t)ATT_KEYS * (a->dim + 8) + (size_t)a->vdim * (ATT_KEYS + 8))
                          : sizeof(float) * ((size_t)ATT_PAIRS * a->dim + (size_t)ATT_KEYS * (a->dim + 4) + (size_t)ATT_KEYS * a->vdim + ATT_PAIRS * ATT_KEYS);
-  if (smem > 227 * 1024) return THA_STATUS_NOT_SUPPORTED;
+  if (!wide && smem > 227 * 1024) return THA_STATUS_NOT_SUPPORTED;
   // position tiles: at most one ragged tile per sequence beyond rows / AP
   const int tiles = rows->n_rows / AP + rows->n_seqs;
   // few blocks and many keys (decoding at long contexts): deal the key tiles of a block to several
@@ -1455,18 +1464,31 @@ extern "C" int tha_hyb_attn(void* stream, int dtype, const tha_attn_t* a, const 
   const dim3 grid(tiles * splits, a->kv_heads, ceil_div(gsize, AG));
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == THA_DT_BF16) {
-    if (tc) {
+    if (wide) {
+      const int st = hyb_attn_wide_launch(s, a, rows, kv, q, (bf16*)out, grid, pairs, AG, AP, splits, split_scratch);
+      if (st != THA_STATUS_SUCCESS) return st;
+    } else if (tc) {
       THA_CUDA_OK(launch(hyb_attn_mma_kernel, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, (bf16*)out, AG, AP, splits, split_scratch));
     } else {
-      if (smem > 48 * 1024) THA_CUDA_OK(cudaFuncSetAttribute(hyb_attn_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      THA_CUDA_OK(launch(hyb_attn_kernel<bf16>, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, (bf16*)out, AG, AP, splits, split_scratch));
+      if (a->vdim <= 256) {
+        if (smem > 48 * 1024) THA_CUDA_OK(cudaFuncSetAttribute(hyb_attn_kernel<bf16, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        THA_CUDA_OK(launch(hyb_attn_kernel<bf16, 8>, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, (bf16*)out, AG, AP, splits, split_scratch));
+      } else {
+        if (smem > 48 * 1024) THA_CUDA_OK(cudaFuncSetAttribute(hyb_attn_kernel<bf16, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        THA_CUDA_OK(launch(hyb_attn_kernel<bf16, 16>, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, (bf16*)out, AG, AP, splits, split_scratch));
+      }
     }
     if (splits > 1)
       THA_CUDA_OK(launch(hyb_attn_merge_kernel<bf16>, dim3(ceil_div(rows->n_rows * a->heads, 4)), dim3(128), 0, s, false, (bf16*)out,
                          (const float*)split_scratch, rows->n_rows, a->heads, a->vdim, splits));
   } else {
-    if (smem > 48 * 1024) THA_CUDA_OK(cudaFuncSetAttribute(hyb_attn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    THA_CUDA_OK(launch(hyb_attn_kernel<float>, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, (float*)out, AG, AP, splits, split_scratch));
+    if (a->vdim <= 256) {
+      if (smem > 48 * 1024) THA_CUDA_OK(cudaFuncSetAttribute(hyb_attn_kernel<float, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      THA_CUDA_OK(launch(hyb_attn_kernel<float, 8>, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, (float*)out, AG, AP, splits, split_scratch));
+    } else {
+      if (smem > 48 * 1024) THA_CUDA_OK(cudaFuncSetAttribute(hyb_attn_kernel<float, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      THA_CUDA_OK(launch(hyb_attn_kernel<float, 16>, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, (float*)out, AG, AP, splits, split_scratch));
+    }
     if (splits > 1)
       THA_CUDA_OK(launch(hyb_attn_merge_kernel<float>, dim3(ceil_div(rows->n_rows * a->heads, 4)), dim3(128), 0, s, false, (float*)out,
                          (const float*)split_scratch, rows->n_rows, a->heads, a->vdim, splits));

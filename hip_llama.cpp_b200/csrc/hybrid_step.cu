@@ -273,7 +273,7 @@ extern "C" int tha_hyb_step(void* stream, const tha_hyb_model_t* m, const tha_ro
       // one key/value head over the cached rows [latent | rotated part]; the values are the latent itself
       tha_attn_t at = {};
       at.heads = a.heads; at.kv_heads = 1; at.dim = DA; at.vdim = a.kv_rank; at.rot = -1; at.unit_rms = 0; at.eps = a.eps;
-      at.scale = a.scale; at.chunk = 0; at.cache_layer = a.cache_layer;
+      at.scale = a.scale; at.chunk = 0; at.cache_layer = a.cache_layer; at.values_in_keys = 1;
       tha_kv_t lkv = *kv;
       lkv.v_pool = kv->k_pool;
       HYB_OK(tha_hyb_attn(stream, dt, &at, rows, &lkv, b.q, b.abuf, b.split_floats ? b.split : nullptr, b.split_floats));

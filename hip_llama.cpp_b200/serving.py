@@ -238,3 +238,70 @@ def random_timerax_tensors(cfg: dict, seed: int = 0) -> dict:
             a = 1.0 + rng.standard_normal(shape) * 0.1
         out[name] = a.astype(np.float32)
     return out
+
+
+def numizen_tensor_shapes(cfg: dict, decay_rank: int = 64) -> dict:
+    """name -> shape of every tensor a Numizen config asks for (decay_rank: rows of the gla mixers' first decay
+    projection, a property of the tensors and not of the config)."""
+    W, V = cfg["width"], cfg["vocab"]
+    s = {"embed": (V, W), "pos": (cfg["max_positions"], W), "head": (V, W)}
+
+    def norm(n):
+        s[n], s[n + ".b"], s[n + ".alpha"] = (W,), (W,), ()
+
+    norm("final.norm")
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        norm(p + "norm1")
+        norm(p + "norm2")
+        s[p + "ls1"] = s[p + "ls2"] = (W,)
+        q = p + "mix."
+        if L["type"] == "latent_attention":
+            H, D, R, E = m["heads"], m["dim"], m["rot_dim"], m["vdim"]
+            s[q + "dq"], s[q + "dq.norm"], s[q + "uq"] = (m["q_rank"], W), (m["q_rank"],), (H * (D + R), m["q_rank"])
+            s[q + "dkv"], s[q + "dkv.norm"] = (m["kv_rank"] + R, W), (m["kv_rank"],)
+            s[q + "uk"], s[q + "uv"] = (H * D, m["kv_rank"]), (H * E, m["kv_rank"])
+            s[q + "g"], s[q + "o"] = (H * E, W), (W, H * E)
+        else:
+            H, D, E = m["heads"], m["dim"], m["vdim"]
+            s[q + "q"] = s[q + "k"] = (H * D, W)
+            s[q + "v"] = s[q + "g"] = (H * E, W)
+            s[q + "o"], s[q + "norm"] = (W, H * E), (E,)
+            s[q + "a1"], s[q + "a2"], s[q + "a2.b"] = (decay_rank, W), (H * D, decay_rank), (H * D,)
+        f = L.get("mlp")
+        if not f:
+            continue
+        q = p + "mlp."
+        if f["kind"] == "dense":
+            s[q + "gate"] = s[q + "up"] = (f["ff"], W)
+            s[q + "down"] = (W, f["ff"])
+        else:
+            for e in range(f["router"]["experts"]):
+                s[q + f"e{e}.up"], s[q + f"e{e}.down"] = (f["expert"]["ff"], W), (W, f["expert"]["ff"])
+            s[q + "router"], s[q + "correction"] = (f["router"]["experts"], W), (f["router"]["experts"],)
+            if f.get("shared"):
+                s[q + "shared.up"], s[q + "shared.down"], s[q + "shared.sg"] = (f["shared"]["ff"], W), (W, f["shared"]["ff"]), (1, W)
+    return s
+
+
+def random_numizen_tensors(cfg: dict, seed: int = 0, decay_rank: int = 64) -> dict:
+    """Random weights of a Numizen config: matrices N(0, 1/in), norm weights and layer scales around one, norm scalars
+    in (0.5, 1), small router corrections, decay biases where the memory neither freezes nor forgets at once."""
+    rng = np.random.default_rng(seed)
+    out = {}
+    for name, shape in numizen_tensor_shapes(cfg, decay_rank).items():
+        last = name.rsplit(".", 1)[-1]
+        if last == "alpha":
+            a = np.array(rng.uniform(0.5, 1.0))
+        elif name.endswith("a2.b"):
+            a = 2.0 + rng.standard_normal(shape)
+        elif last == "b":
+            a = 0.1 * rng.standard_normal(shape)
+        elif last == "correction":
+            a = 0.05 * rng.standard_normal(shape)
+        elif len(shape) == 2:
+            a = rng.standard_normal(shape, dtype=np.float32) * (1.0 if name == "embed" else 0.3 if name == "pos" else 1.0 / np.sqrt(shape[1]))
+        else:
+            a = 1.0 + 0.2 * rng.standard_normal(shape)
+        out[name] = np.asarray(a, dtype=np.float32)
+    return out

@@ -110,6 +110,8 @@ typedef struct {
   int cache_layer;  /* which layer of the pool holds this layer's rows */
   int o_q, o_k, o_v; /* columns of the stacked input projection */
   const void* w_o;  /* [width, heads * vdim] */
+  int values_in_keys; /* 1: a value row is the first vdim channels of its key row (vdim <= dim): callers pass the K pool as
+                         v_pool as well, and kernels may stage one tile for both */
 } tha_attn_t;
 
 /* Matrix memory with exponential input gate, sigmoid forget gate (both in log space, soft-capped) and a running

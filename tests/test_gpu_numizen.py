@@ -388,6 +388,32 @@ def test_one_far_key_among_hundreds(tmp_path, dtype, decoded):
         assert rel_err(got[690], z[690]) < min(BF16_TOL, moved / 2)
 
 
+@pytest.mark.parametrize("cuts", [[300], [150, 86, 2, 1], [64, 1]])
+def test_wide_latent_bfloat16_every_position(tmp_path, cuts):
+    """A cached row of more than 128 channels takes, in bfloat16, the attention form in which a block of warps shares the
+    query rows and the output (whole prompts: 64 pairs per block; single tokens: 16; few rows at a long context: cut along
+    the keys and merged).  Peaked scores and a check of EVERY position by itself: a key too many or too few, or a tile of
+    keys lost, is an error of tens of percent there."""
+    cfg = model([latent(None, heads=4, dim=24, rot_dim=32, vdim=16, q_rank=48, kv_rank=160, scale=0.5)], width=64, vocab=200)
+    b = Built(tmp_path, cfg, 41)
+    n = 300
+    toks = tokens_for(b, n, 3)
+    _, layers = b.ref(toks)
+    base = O.embed(b.cfg, b.w, toks)
+    mix = layers[0] - base
+    e = b.engine("bfloat16")
+    at, got, i = 0, [], 0
+    while at < n:
+        c = min(cuts[min(i, len(cuts) - 1)], n - at)
+        got.append(e.step([("a", toks[at:at + c], [])], taps=True)[1][0])
+        at += c
+        i += 1
+    got = np.concatenate(got, 0) - base
+    worst = max(rel_err(got[p], mix[p]) for p in range(n))
+    assert worst < 6e-2, worst
+    assert rel_err(got, mix) < 2e-2
+
+
 # ---- other sizes: values that are often equal, or 1 ------------------------------------------------------------------
 @pytest.mark.parametrize("case", ["single", "wide_heads", "everything_small", "loop_all_twice", "loop_nothing", "odd_sizes", "no_loop_key"])
 def test_other_sizes(tmp_path, case):
