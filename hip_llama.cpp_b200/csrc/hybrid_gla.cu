@@ -2,7 +2,7 @@
 //   hyb_gla_decay_kernel   all rows at once, in place: z + b -> a = sigmoid(z + b)^(1/tau) = exp(-softplus(-(z + b)) / tau)
 //   hyb_gla_scan_kernel    the recurrence with the state in registers: a warp owns GLA_COLS value columns of one
 //                          (sequence, head), lane l the key channels l, l + 32, ...; the column sums S^T q are warp
-//                          shuffles, the next token's inputs are fetched while the current one is computed; no barrier.
+//                          shuffles, a token's inputs are fetched several tokens ahead into a ring of registers; no barrier.
 //                          The state is read from the sequence's slot before its first row of the step and written back
 //                          after its last, so a prompt cut anywhere continues exactly where it stopped.
 // Decays, state and read-out are fp32 in both number formats; the head norm and the silu gate follow in
@@ -24,7 +24,7 @@ __global__ void hyb_gla_decay_kernel(float* __restrict__ z, size_t n, int hd, co
   z[i] = expf(-hyb_softplus(-v) * inv_tau);
 }
 
-template <int RPL>
+template <int RPL, int AHEAD>
 __global__ void __launch_bounds__(32 * GLA_WARPS) hyb_gla_scan_kernel(tha_gla_t g, tha_rows_t rows, tha_state_store_t st,
                                                                       const float* __restrict__ proj, long long ldp,
                                                                       const float* __restrict__ decay, float* __restrict__ o_raw) {
@@ -42,38 +42,54 @@ __global__ void __launch_bounds__(32 * GLA_WARPS) hyb_gla_scan_kernel(tha_gla_t 
   }
   const float qscale = 1.0f / sqrtf((float)D);
   const int r_begin = rows.seq_first[s], r_end = rows.seq_first[s + 1];
-  float q[RPL], k[RPL], a[RPL], v[GLA_COLS];
-  auto fetch = [&](int r) {
+  // a token's inputs are loaded AHEAD tokens before they are used (a ring of register sets, the loop unrolled over it)
+  struct In { float q[RPL], k[RPL], a[RPL], v[GLA_COLS]; };
+  In ring[AHEAD];
+  auto fetch = [&](int r, In& in) {
     const float* x = proj + (size_t)r * ldp;
 #pragma unroll
     for (int i = 0; i < RPL; i++) {
       const int d = lane + 32 * i;
-      q[i] = d < D ? x[g.o_q + h * D + d] * qscale : 0.f;
-      k[i] = d < D ? x[g.o_k + h * D + d] : 0.f;
-      a[i] = d < D ? decay[(size_t)r * g.heads * D + h * D + d] : 0.f;
+      in.q[i] = d < D ? x[g.o_q + h * D + d] : 0.f;
+      in.k[i] = d < D ? x[g.o_k + h * D + d] : 0.f;
+      in.a[i] = d < D ? decay[(size_t)r * g.heads * D + h * D + d] : 0.f;
     }
 #pragma unroll
-    for (int c = 0; c < GLA_COLS; c++) v[c] = e0 + c < E ? x[g.o_v + h * E + e0 + c] : 0.f;
+    for (int c = 0; c < GLA_COLS; c++) in.v[c] = e0 + c < E ? x[g.o_v + h * E + e0 + c] : 0.f;
   };
-  if (r_begin < r_end) fetch(r_begin);
-  for (int r = r_begin; r < r_end; r++) {
-    float o[GLA_COLS];
 #pragma unroll
-    for (int c = 0; c < GLA_COLS; c++) o[c] = 0.f;
+  for (int u = 0; u < AHEAD; u++)
+    if (r_begin + u < r_end) fetch(r_begin + u, ring[u]);
+  // one token; `refill` (a row, or -1) is what the token's ring entry is loaded with once its values are taken
+  auto token = [&](int r, In& in, int refill) {
+    float cq[RPL], ck[RPL], ca[RPL], cv[GLA_COLS], o[GLA_COLS];
+#pragma unroll
+    for (int i = 0; i < RPL; i++) { cq[i] = in.q[i] * qscale; ck[i] = in.k[i]; ca[i] = in.a[i]; }
+#pragma unroll
+    for (int c = 0; c < GLA_COLS; c++) { cv[c] = in.v[c]; o[c] = 0.f; }
+    if (refill >= 0) fetch(refill, in);
 #pragma unroll
     for (int i = 0; i < RPL; i++)
 #pragma unroll
       for (int c = 0; c < GLA_COLS; c++) {
-        S[i][c] = fmaf(S[i][c], a[i], k[i] * v[c]);
-        o[c] = fmaf(S[i][c], q[i], o[c]);
+        S[i][c] = fmaf(S[i][c], ca[i], ck[i] * cv[c]);
+        o[c] = fmaf(S[i][c], cq[i], o[c]);
       }
-    if (r + 1 < r_end) fetch(r + 1);
 #pragma unroll
     for (int c = 0; c < GLA_COLS; c++) {
       const float ov = warp_sum(o[c]);
       if (lane == c && e0 + c < E) o_raw[(size_t)r * g.heads * E + (size_t)h * E + e0 + c] = ov;
     }
+  };
+  // whole groups without a branch between their tokens (the refill row is clamped instead of tested), then the ragged end
+  int rb = r_begin;
+  for (; rb + AHEAD <= r_end; rb += AHEAD) {
+#pragma unroll
+    for (int u = 0; u < AHEAD; u++) token(rb + u, ring[u], min(rb + u + AHEAD, r_end - 1));
   }
+#pragma unroll
+  for (int u = 0; u < AHEAD; u++)
+    if (rb + u < r_end) token(rb + u, ring[u], -1);
 #pragma unroll
   for (int i = 0; i < RPL; i++) {
     const int d = lane + 32 * i;
@@ -99,12 +115,12 @@ extern "C" int tha_hyb_gla_scan(void* stream, int dtype, const tha_gla_t* g, con
                      1.0f / g->tau));
   const dim3 grid(rows->n_seqs, g->heads, ceil_div(g->vdim, GLA_COLS * GLA_WARPS)), block(32 * GLA_WARPS);
   const float* dec = z_raw;
-#define GLA_LAUNCH(R) THA_CUDA_OK(launch(hyb_gla_scan_kernel<R>, grid, block, 0, s, false, *g, *rows, *st, proj, ldp, dec, o_raw))
-  if (g->dim <= 32) GLA_LAUNCH(1);
-  else if (g->dim <= 64) GLA_LAUNCH(2);
-  else if (g->dim <= 128) GLA_LAUNCH(4);
-  else if (g->dim <= 256) GLA_LAUNCH(8);
-  else GLA_LAUNCH(16);
+#define GLA_LAUNCH(R, A) THA_CUDA_OK(launch(hyb_gla_scan_kernel<R, A>, grid, block, 0, s, false, *g, *rows, *st, proj, ldp, dec, o_raw))
+  if (g->dim <= 32) GLA_LAUNCH(1, 4);
+  else if (g->dim <= 64) GLA_LAUNCH(2, 4);
+  else if (g->dim <= 128) GLA_LAUNCH(4, 4);
+  else if (g->dim <= 256) GLA_LAUNCH(8, 2);
+  else GLA_LAUNCH(16, 1);
 #undef GLA_LAUNCH
   return tha_hyb_head_gate(stream, dtype, out, o_raw, rows->n_rows, g->heads, g->vdim, 1, g->eps, g->norm, 0, proj + g->o_g, ldp, THA_GATE_SILU);
 }

@@ -168,12 +168,12 @@ __global__ void __launch_bounds__(128 * MT) hyb_attn_wide_kernel(tha_attn_t a, t
       const int t = kt + j;
       const bool live = t <= p_last;
       const float* src = kv.k_pool + (live ? hyb_kv_row(kv, slot, t, a.cache_layer) : 0) + (size_t)g * D;
-      for (int d0 = 0; d0 < D; d0 += 128) {
-        float buf[4];
+      for (int d0 = 0; d0 < D; d0 += 320) {   // ten loads per lane in flight
+        float buf[10];
 #pragma unroll
-        for (int c = 0; c < 4; c++) { const int d = d0 + lane + 32 * c; buf[c] = (live && d < D) ? __ldg(src + d) : 0.f; }
+        for (int c = 0; c < 10; c++) { const int d = d0 + lane + 32 * c; buf[c] = (live && d < D) ? __ldg(src + d) : 0.f; }
 #pragma unroll
-        for (int c = 0; c < 4; c++) { const int d = d0 + lane + 32 * c; if (d < D) Ks[(size_t)j * DS + d] = __float2bfloat16_rn(buf[c]); }
+        for (int c = 0; c < 10; c++) { const int d = d0 + lane + 32 * c; if (d < D) Ks[(size_t)j * DS + d] = __float2bfloat16_rn(buf[c]); }
       }
     }
     __syncthreads();
