@@ -7,6 +7,7 @@
 // The attention itself is tha_hyb_attn with one key/value head whose values are the first kv_rank channels of its keys.
 // Norms, rotation and the cache are fp32 in both number formats.
 #include <cuda_bf16.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "hybrid_ops.cuh"
@@ -82,10 +83,11 @@ __global__ void hyb_latent_split_q_kernel(tha_latent_t a, int n_rows, const floa
 // that width, so a block shares them: 16 * MT (position, query head) pairs, 4 * MT warps; warp (mi, ei) owns row tile
 // mi (16 pairs) and slice ei of four.  Per tile of 32 keys (aligned to absolute multiples of 32, like the other forms):
 //   1. the tile's key rows go to shared memory once, as bf16 -- they are also the values;
-//   2. warp (mi, ei): scores of its 16 pairs against keys 8 ei .. 8 ei + 7 (mma.sync m16n8k16, queries and keys from
-//      shared memory), written to shared memory in fp32;
-//   3. a warp takes 4 pairs (lane = key): scale, mask, running maximum and sum in fp32, weights rounded to bf16 (the sums
-//      add the rounded weights), the rescale factor of each pair;
+//   2. warp (mi, ei): scores of its 16 pairs against the 32 keys over a quarter of the channels (mma.sync m16n8k16; the
+//      query fragment and the key fragments of two 8-key tiles come from shared memory by ldmatrix.x4), written to shared
+//      memory in fp32 as one of four shares;
+//   3. a warp takes 4 pairs (lane = key): sum of the shares in a fixed order, scale, mask, running maximum and sum in
+//      fp32, weights rounded to bf16 (the sums add the rounded weights), the rescale factor of each pair;
 //   4. warp (mi, ei): rescales its accumulators [16 pairs, vdim / 4 channels] and adds weights x values; the value
 //      fragments come out of the row-major key tile through ldmatrix.trans.
 // Three block barriers per tile.  Splits along the keys and their merge as in the other forms.
@@ -96,6 +98,11 @@ __device__ __forceinline__ void mma_bf16_m16n8k16(float (&c)[4], const uint32_t 
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
 }
 
 template <int MT>
@@ -109,8 +116,8 @@ __global__ void __launch_bounds__(128 * MT) hyb_attn_wide_kernel(tha_attn_t a, t
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smraw);          // [PAIRS][DS]
   __nv_bfloat16* Ks = Qs + (size_t)PAIRS * DS;                             // [32][DS]
   __nv_bfloat16* Pb = Ks + (size_t)WK_KEYS * DS;                           // [PAIRS][40] weights
-  float* Sf = reinterpret_cast<float*>(Pb + PAIRS * 40);                   // [PAIRS][33] scores
-  float* corr_s = Sf + PAIRS * 33;                                         // [PAIRS] rescale factors, then 1 / sum
+  float* Sf = reinterpret_cast<float*>(Pb + PAIRS * 40);                   // [4][PAIRS][33] partial scores
+  float* corr_s = Sf + 4 * PAIRS * 33;                                       // [PAIRS] rescale factors, then 1 / sum
   float* m_s = corr_s + PAIRS;                                             // [PAIRS] running maxima at the end
   int seq = -1, r0 = 0, r_end = 0;
   {
@@ -160,7 +167,9 @@ __global__ void __launch_bounds__(128 * MT) hyb_attn_wide_kernel(tha_attn_t a, t
     kt_last = min(p_last, (sp + 1) * per * WK_KEYS - 1);
     kt_begin = sp * per * WK_KEYS;
   }
-  const unsigned ks_base = (unsigned)__cvta_generic_to_shared(Ks);
+  // cache rows start on 16-byte boundaries when the pool's row pitch and the head's offset are multiples of four floats
+  const bool vec4 = (kv.kv_dim & 3) == 0 && (D & 3) == 0 && (reinterpret_cast<size_t>(kv.k_pool) & 15) == 0;
+  const unsigned ks_base = (unsigned)__cvta_generic_to_shared(Ks), qs_base = (unsigned)__cvta_generic_to_shared(Qs);
   for (int kt = kt_begin; kt <= kt_last; kt += WK_KEYS) {
     __syncthreads();   // the previous tile's weights and values have been used (first pass: the queries are in place)
     // 1. the tile's key rows; keys past the last position of the block are zero
@@ -168,33 +177,66 @@ __global__ void __launch_bounds__(128 * MT) hyb_attn_wide_kernel(tha_attn_t a, t
       const int t = kt + j;
       const bool live = t <= p_last;
       const float* src = kv.k_pool + (live ? hyb_kv_row(kv, slot, t, a.cache_layer) : 0) + (size_t)g * D;
-      for (int d0 = 0; d0 < D; d0 += 320) {   // ten loads per lane in flight
-        float buf[10];
+      if (vec4) {   // 16-byte aligned rows: five 128-bit loads per lane in flight, four bf16 per store
+        const float4* src4 = reinterpret_cast<const float4*>(src);
+        const int D4 = D >> 2;
+        for (int i0 = 0; i0 < D4; i0 += 160) {
+          float4 buf[5];
 #pragma unroll
-        for (int c = 0; c < 10; c++) { const int d = d0 + lane + 32 * c; buf[c] = (live && d < D) ? __ldg(src + d) : 0.f; }
+          for (int c = 0; c < 5; c++) { const int i = i0 + lane + 32 * c; buf[c] = (live && i < D4) ? __ldg(src4 + i) : make_float4(0.f, 0.f, 0.f, 0.f); }
 #pragma unroll
-        for (int c = 0; c < 10; c++) { const int d = d0 + lane + 32 * c; if (d < D) Ks[(size_t)j * DS + d] = __float2bfloat16_rn(buf[c]); }
+          for (int c = 0; c < 5; c++) {
+            const int i = i0 + lane + 32 * c;
+            if (i < D4) {
+              uint2 pk;
+              pk.x = pack2_bf16(buf[c].x, buf[c].y);
+              pk.y = pack2_bf16(buf[c].z, buf[c].w);
+              *reinterpret_cast<uint2*>(Ks + (size_t)j * DS + 4 * i) = pk;
+            }
+          }
+        }
+      } else {
+        for (int d0 = 0; d0 < D; d0 += 320) {   // ten loads per lane in flight
+          float buf[10];
+#pragma unroll
+          for (int c = 0; c < 10; c++) { const int d = d0 + lane + 32 * c; buf[c] = (live && d < D) ? __ldg(src + d) : 0.f; }
+#pragma unroll
+          for (int c = 0; c < 10; c++) { const int d = d0 + lane + 32 * c; if (d < D) Ks[(size_t)j * DS + d] = __float2bfloat16_rn(buf[c]); }
+        }
       }
     }
     __syncthreads();
-    // 2. scores of row tile mi against keys 8 ei .. 8 ei + 7
+    // 2. partial scores of row tile mi against all 32 keys over this warp's share of the channels (k steps ei, ei + 4, ...);
+    //    a whole query fragment and the key fragments of two 8-key tiles per ldmatrix
     {
-      float sacc[4] = {0.f, 0.f, 0.f, 0.f};
-      const __nv_bfloat16* qa = Qs + (size_t)(mi * 16 + lr) * DS + lc;
-      const __nv_bfloat16* kb = Ks + (size_t)(ei * 8 + lr) * DS + lc;
-      for (int k0 = 0; k0 < D; k0 += 16) {
-        uint32_t af[4], bf[2];
-        af[0] = *reinterpret_cast<const uint32_t*>(qa + k0);
-        af[1] = *reinterpret_cast<const uint32_t*>(qa + 8 * DS + k0);
-        af[2] = *reinterpret_cast<const uint32_t*>(qa + k0 + 8);
-        af[3] = *reinterpret_cast<const uint32_t*>(qa + 8 * DS + k0 + 8);
-        bf[0] = *reinterpret_cast<const uint32_t*>(kb + k0);
-        bf[1] = *reinterpret_cast<const uint32_t*>(kb + k0 + 8);
-        mma_bf16_m16n8k16(sacc, af, bf);
+      float sacc[4][4];
+#pragma unroll
+      for (int j = 0; j < 4; j++)
+#pragma unroll
+        for (int v = 0; v < 4; v++) sacc[j][v] = 0.f;
+      const unsigned a_addr = qs_base + (unsigned)(((size_t)(mi * 16 + (lane & 15)) * DS + (lane >> 4) * 8) * sizeof(__nv_bfloat16));
+      const unsigned b_addr = ks_base + (unsigned)(((size_t)((lane & 7) + ((lane >> 4) << 3)) * DS + ((lane >> 3) & 1) * 8) * sizeof(__nv_bfloat16));
+      for (int ks = ei; ks < D / 16; ks += 4) {
+        uint32_t af[4];
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(af[0]), "=r"(af[1]), "=r"(af[2]), "=r"(af[3]) : "r"(a_addr + ks * 32));
+#pragma unroll
+        for (int j2 = 0; j2 < 2; j2++) {
+          uint32_t bq[4];
+          asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(bq[0]), "=r"(bq[1]), "=r"(bq[2]), "=r"(bq[3])
+                       : "r"(b_addr + (unsigned)(j2 * 16 * DS * sizeof(__nv_bfloat16)) + ks * 32));
+          const uint32_t b0[2] = {bq[0], bq[1]}, b1[2] = {bq[2], bq[3]};
+          mma_bf16_m16n8k16(sacc[2 * j2], af, b0);
+          mma_bf16_m16n8k16(sacc[2 * j2 + 1], af, b1);
+        }
       }
-      float* sr = Sf + (mi * 16 + lr) * 33 + ei * 8 + lc;
-      sr[0] = sacc[0]; sr[1] = sacc[1];
-      sr[8 * 33] = sacc[2]; sr[8 * 33 + 1] = sacc[3];
+      float* sr = Sf + (size_t)ei * PAIRS * 33 + (mi * 16 + lr) * 33 + lc;
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        sr[8 * j] = sacc[j][0]; sr[8 * j + 1] = sacc[j][1];
+        sr[8 * 33 + 8 * j] = sacc[j][2]; sr[8 * 33 + 8 * j + 1] = sacc[j][3];
+      }
     }
     __syncthreads();
     // 3. online softmax of this warp's 4 pairs, lane = key
@@ -202,7 +244,8 @@ __global__ void __launch_bounds__(128 * MT) hyb_attn_wide_kernel(tha_attn_t a, t
     for (int rr = 0; rr < 4; rr++) {
       const int pr = warp * 4 + rr, t = kt + lane;
       const bool vis = s_ok[rr] && t <= s_pos[rr];
-      const float sv = vis ? Sf[pr * 33 + lane] * a.scale : -INFINITY;
+      const float* sp = Sf + pr * 33 + lane;   // the four channel shares, summed in a fixed order
+      const float sv = vis ? ((sp[0] + sp[PAIRS * 33]) + (sp[2 * PAIRS * 33] + sp[3 * PAIRS * 33])) * a.scale : -INFINITY;
       const float m_new = fmaxf(m_run[rr], warp_max(sv));
       float p = 0.f, corr = 1.f;
       if (m_new > -INFINITY) {
@@ -229,16 +272,23 @@ __global__ void __launch_bounds__(128 * MT) hyb_attn_wide_kernel(tha_attn_t a, t
         pf[t2][3] = *reinterpret_cast<const uint32_t*>(pa + 8 * 40 + 16 * t2 + 8);
       }
 #pragma unroll
-      for (int n = 0; n < WK_MAX_SLICE / 8; n++) {
+      for (int n = 0; n < WK_MAX_SLICE / 8; n += 2) {
         if (8 * n < ES) {
+          const bool two = 8 * (n + 1) < ES;
           oacc[n][0] *= ca; oacc[n][1] *= ca; oacc[n][2] *= cb; oacc[n][3] *= cb;
+          if (two) { oacc[n + 1][0] *= ca; oacc[n + 1][1] *= ca; oacc[n + 1][2] *= cb; oacc[n + 1][3] *= cb; }
 #pragma unroll
           for (int t2 = 0; t2 < 2; t2++) {
-            // values [key][channel] row-major: lanes 0..15 name the rows of keys 16 t2 + (lane & 15); transposed on the way
-            uint32_t vf[2];
-            const unsigned addr = ks_base + (unsigned)(((size_t)(16 * t2 + (lane & 15)) * DS + ei * ES + 8 * n) * sizeof(__nv_bfloat16));
-            asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];" : "=r"(vf[0]), "=r"(vf[1]) : "r"(addr));
-            mma_bf16_m16n8k16(oacc[n], pf[t2], vf);
+            // values [key][channel] row-major, transposed on the way: lanes 0..15 name the rows of keys 16 t2 + (lane & 15) at
+            // this channel tile, lanes 16..31 the same keys at the next one (an odd last tile reads its own twice)
+            uint32_t vf[4];
+            const int ch = ei * ES + 8 * n + ((two && lane >= 16) ? 8 : 0);
+            const unsigned addr = ks_base + (unsigned)(((size_t)(16 * t2 + (lane & 15)) * DS + ch) * sizeof(__nv_bfloat16));
+            asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(vf[0]), "=r"(vf[1]), "=r"(vf[2]), "=r"(vf[3]) : "r"(addr));
+            const uint32_t v0[2] = {vf[0], vf[1]}, v1[2] = {vf[2], vf[3]};
+            mma_bf16_m16n8k16(oacc[n], pf[t2], v0);
+            if (two) mma_bf16_m16n8k16(oacc[n + 1], pf[t2], v1);
           }
         }
       }
@@ -274,7 +324,7 @@ __global__ void __launch_bounds__(128 * MT) hyb_attn_wide_kernel(tha_attn_t a, t
 }
 
 static size_t wide_smem(const tha_attn_t* a, int pairs) {
-  return sizeof(__nv_bfloat16) * ((size_t)(pairs + WK_KEYS) * (a->dim + 8) + (size_t)pairs * 40) + sizeof(float) * ((size_t)pairs * 33 + 2 * pairs);
+  return sizeof(__nv_bfloat16) * ((size_t)(pairs + WK_KEYS) * (a->dim + 8) + (size_t)pairs * 40) + sizeof(float) * ((size_t)4 * pairs * 33 + 2 * pairs);
 }
 
 // one key/value head, key rows a multiple of 16 wide, values inside them, four slices of at most 128 channels that are multiples of 8, no
@@ -285,6 +335,9 @@ bool hyb_attn_wide_ok(const tha_attn_t* a) {
 }
 // 64 pairs per block when the step has prompt portions that fill them, else 16
 int hyb_attn_wide_pairs(const tha_attn_t* a, const tha_rows_t* rows) {
+  static int forced = -1;   // THA_WIDE_PAIRS=16|32|64 fixes the block size (A/B aid)
+  if (forced < 0) { const char* v = getenv("THA_WIDE_PAIRS"); forced = (v && *v) ? atoi(v) : 0; }
+  if (forced == 16 || forced == 32 || forced == 64) return forced;
   const long long per_seq = (long long)rows->max_seq_rows * (a->heads / a->kv_heads);
   return per_seq >= 64 ? 64 : 16;
 }
@@ -294,6 +347,9 @@ int hyb_attn_wide_launch(cudaStream_t s, const tha_attn_t* a, const tha_rows_t* 
   if (pairs == 64) {
     THA_CUDA_OK(cudaFuncSetAttribute(hyb_attn_wide_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     THA_CUDA_OK(launch(hyb_attn_wide_kernel<4>, grid, dim3(512), smem, s, false, *a, *rows, *kv, q, out, AG, AP, splits, partial));
+  } else if (pairs == 32) {
+    THA_CUDA_OK(cudaFuncSetAttribute(hyb_attn_wide_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    THA_CUDA_OK(launch(hyb_attn_wide_kernel<2>, grid, dim3(256), smem, s, false, *a, *rows, *kv, q, out, AG, AP, splits, partial));
   } else {
     THA_CUDA_OK(cudaFuncSetAttribute(hyb_attn_wide_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     THA_CUDA_OK(launch(hyb_attn_wide_kernel<1>, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, out, AG, AP, splits, partial));
