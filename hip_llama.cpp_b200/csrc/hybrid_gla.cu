@@ -3,11 +3,13 @@
 //   hyb_gla_scan_kernel    the recurrence with the state in registers: a warp owns GLA_COLS value columns of one
 //                          (sequence, head), lane l the key channels l, l + 32, ...; the column sums S^T q are warp
 //                          shuffles, a token's inputs are fetched several tokens ahead into a ring of registers; no barrier.
-//                          The state is read from the sequence's slot before its first row of the step and written back
+//                          The state of a head lies in the slot as [column pair][key channel][2] (a warp's share is one
+//                          contiguous run).  It is read from the sequence's slot before its first row of the step and written back
 //                          after its last, so a prompt cut anywhere continues exactly where it stopped.
 // Decays, state and read-out are fp32 in both number formats; the head norm and the silu gate follow in
 // tha_hyb_head_gate.
 #include <cuda_bf16.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "hybrid_ops.cuh"
@@ -15,7 +17,7 @@
 
 namespace tha {
 
-constexpr int GLA_COLS = 2, GLA_WARPS = 4;
+constexpr int GLA_WARPS = 4, GLA_STATE_PAD = 8;   // a head's value columns are padded to a multiple of 8 in the slot
 
 __global__ void hyb_gla_decay_kernel(float* __restrict__ z, size_t n, int hd, const float* __restrict__ bias, float inv_tau) {
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -24,7 +26,7 @@ __global__ void hyb_gla_decay_kernel(float* __restrict__ z, size_t n, int hd, co
   z[i] = expf(-hyb_softplus(-v) * inv_tau);
 }
 
-template <int RPL, int AHEAD>
+template <int RPL, int AHEAD, int GLA_COLS>
 __global__ void __launch_bounds__(32 * GLA_WARPS) hyb_gla_scan_kernel(tha_gla_t g, tha_rows_t rows, tha_state_store_t st,
                                                                       const float* __restrict__ proj, long long ldp,
                                                                       const float* __restrict__ decay, float* __restrict__ o_raw) {
@@ -32,13 +34,15 @@ __global__ void __launch_bounds__(32 * GLA_WARPS) hyb_gla_scan_kernel(tha_gla_t 
   const int D = g.dim, E = g.vdim;
   const int e0 = (blockIdx.z * GLA_WARPS + warp) * GLA_COLS;
   if (e0 >= E) return;
-  float* gstate = st.base + (size_t)rows.seq_slot[s] * st.slot_floats + g.state_off + (size_t)h * D * E;
+  // the head's state as [column pair][key channel][2]: a warp's share is one contiguous run, a lane's two columns adjacent
+  const int EP = (E + GLA_STATE_PAD - 1) / GLA_STATE_PAD * GLA_STATE_PAD;
+  float* gstate = st.base + (size_t)rows.seq_slot[s] * st.slot_floats + g.state_off + (size_t)h * D * EP + (size_t)(e0 / GLA_COLS) * D * GLA_COLS;
   float S[RPL][GLA_COLS];
 #pragma unroll
   for (int i = 0; i < RPL; i++) {
     const int d = lane + 32 * i;
 #pragma unroll
-    for (int c = 0; c < GLA_COLS; c++) S[i][c] = (d < D && e0 + c < E) ? gstate[(size_t)d * E + e0 + c] : 0.f;
+    for (int c = 0; c < GLA_COLS; c++) S[i][c] = (d < D && e0 + c < E) ? gstate[(size_t)d * GLA_COLS + c] : 0.f;
   }
   const float qscale = 1.0f / sqrtf((float)D);
   const int r_begin = rows.seq_first[s], r_end = rows.seq_first[s + 1];
@@ -75,10 +79,34 @@ __global__ void __launch_bounds__(32 * GLA_WARPS) hyb_gla_scan_kernel(tha_gla_t 
         S[i][c] = fmaf(S[i][c], ca[i], ck[i] * cv[c]);
         o[c] = fmaf(S[i][c], cq[i], o[c]);
       }
+    // the column sums: halve the columns a lane carries while exchanging across lane bits 4, 3, 2 (a lane ends with ONE
+    // column, col = its bits [4 : 4 - log2(COLS)]), then finish over the remaining lane bits
+    int width = GLA_COLS;
 #pragma unroll
-    for (int c = 0; c < GLA_COLS; c++) {
-      const float ov = warp_sum(o[c]);
-      if (lane == c && e0 + c < E) o_raw[(size_t)r * g.heads * E + (size_t)h * E + e0 + c] = ov;
+    for (int off = 16; off >= 4; off >>= 1) {
+      if (width > 1) {
+        const int hw = width / 2;
+        const bool upper = (lane & off) != 0;
+#pragma unroll
+        for (int j = 0; j < GLA_COLS / 2; j++) {
+          if (j < hw) {
+            const float send = upper ? o[j] : o[j + hw];
+            const float keep = upper ? o[j + hw] : o[j];
+            o[j] = keep + __shfl_xor_sync(THA_FULL_MASK, send, off);
+          }
+        }
+        width = hw;
+      } else {
+        o[0] += __shfl_xor_sync(THA_FULL_MASK, o[0], off);
+      }
+    }
+    o[0] += __shfl_xor_sync(THA_FULL_MASK, o[0], 2);
+    o[0] += __shfl_xor_sync(THA_FULL_MASK, o[0], 1);
+    {
+      constexpr int LG = GLA_COLS == 8 ? 3 : GLA_COLS == 4 ? 2 : GLA_COLS == 2 ? 1 : 0;
+      const int col = LG ? (lane >> (5 - LG)) : 0;                 // the column this lane ended with
+      const bool writer = (lane & ((32 >> LG) - 1)) == 0;
+      if (writer && e0 + col < E) o_raw[(size_t)r * g.heads * E + (size_t)h * E + e0 + col] = o[0];
     }
   };
   // whole groups without a branch between their tokens (the refill row is clamped instead of tested), then the ragged end
@@ -96,7 +124,7 @@ __global__ void __launch_bounds__(32 * GLA_WARPS) hyb_gla_scan_kernel(tha_gla_t 
     if (d >= D) continue;
 #pragma unroll
     for (int c = 0; c < GLA_COLS; c++)
-      if (e0 + c < E) gstate[(size_t)d * E + e0 + c] = S[i][c];
+      if (e0 + c < E) gstate[(size_t)d * GLA_COLS + c] = S[i][c];
   }
 }
 
@@ -113,14 +141,19 @@ extern "C" int tha_hyb_gla_scan(void* stream, int dtype, const tha_gla_t* g, con
   const size_t n = (size_t)rows->n_rows * g->heads * g->dim;
   THA_CUDA_OK(launch(hyb_gla_decay_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, false, z_raw, n, g->heads * g->dim, g->b_a2,
                      1.0f / g->tau));
-  const dim3 grid(rows->n_seqs, g->heads, ceil_div(g->vdim, GLA_COLS * GLA_WARPS)), block(32 * GLA_WARPS);
   const float* dec = z_raw;
-#define GLA_LAUNCH(R, A) THA_CUDA_OK(launch(hyb_gla_scan_kernel<R, A>, grid, block, 0, s, false, *g, *rows, *st, proj, ldp, dec, o_raw))
-  if (g->dim <= 32) GLA_LAUNCH(1, 4);
-  else if (g->dim <= 64) GLA_LAUNCH(2, 4);
-  else if (g->dim <= 128) GLA_LAUNCH(4, 4);
-  else if (g->dim <= 256) GLA_LAUNCH(8, 2);
-  else GLA_LAUNCH(16, 1);
+  static int cols_env = -1;   // THA_GLA_COLS=2|4|8: value columns per warp (A/B aid)
+  if (cols_env < 0) { const char* v = getenv("THA_GLA_COLS"); cols_env = (v && *v) ? atoi(v) : 0; }
+  const int cols = (cols_env == 2 || cols_env == 4 || cols_env == 8) && g->dim <= 128 ? cols_env : 2;
+  const dim3 grid(rows->n_seqs, g->heads, ceil_div(g->vdim, cols * GLA_WARPS)), block(32 * GLA_WARPS);
+#define GLA_LAUNCH(R, A, C) THA_CUDA_OK(launch(hyb_gla_scan_kernel<R, A, C>, grid, block, 0, s, false, *g, *rows, *st, proj, ldp, dec, o_raw))
+#define GLA_LAUNCH_COLS(R, A) do { if (cols == 8) GLA_LAUNCH(R, A, 8); else if (cols == 4) GLA_LAUNCH(R, A, 4); else GLA_LAUNCH(R, A, 2); } while (0)
+  if (g->dim <= 32) GLA_LAUNCH_COLS(1, 4);
+  else if (g->dim <= 64) GLA_LAUNCH_COLS(2, 4);
+  else if (g->dim <= 128) GLA_LAUNCH_COLS(4, 4);
+  else if (g->dim <= 256) GLA_LAUNCH(8, 2, 2);
+  else GLA_LAUNCH(16, 1, 2);
+#undef GLA_LAUNCH_COLS
 #undef GLA_LAUNCH
   return tha_hyb_head_gate(stream, dtype, out, o_raw, rows->n_rows, g->heads, g->vdim, 1, g->eps, g->norm, 0, proj + g->o_g, ldp, THA_GATE_SILU);
 }

@@ -43,6 +43,18 @@ __global__ void hyb_dyt_kernel(T* __restrict__ out, const float* __restrict__ x,
   for (int i = threadIdx.x; i < width; i += blockDim.x) hyb_store(out + (size_t)r * width + i, fmaf(tanhf(alpha * xr[i]), w[i], b ? b[i] : 0.f));
 }
 
+// two dynamic-tanh norms of the same row in one pass (the two norms of a parallel block)
+template <typename T>
+__global__ void hyb_dyt2_kernel(T* __restrict__ out1, T* __restrict__ out2, const float* __restrict__ x, tha_norm_t n1, tha_norm_t n2, int width) {
+  const int r = blockIdx.x;
+  const float* xr = x + (size_t)r * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float v = xr[i];
+    hyb_store(out1 + (size_t)r * width + i, fmaf(tanhf(n1.alpha * v), n1.w[i], n1.b ? n1.b[i] : 0.f));
+    hyb_store(out2 + (size_t)r * width + i, fmaf(tanhf(n2.alpha * v), n2.w[i], n2.b ? n2.b[i] : 0.f));
+  }
+}
+
 // ------------------------------------------------------------------------------------------------------------------
 // linear: 64 x 64 output tile per block, 16-deep k slices through shared memory, 4 x 4 per thread, fp32 FMA in
 // ascending k: the sum of an output element is the same whatever tile or group it lands in.
@@ -714,9 +726,12 @@ __global__ void hyb_attn_merge_kernel(T* __restrict__ out, const float* __restri
   for (int s = 0; s < splits; s++) M = fmaxf(M, p0[s * stride + E]);
   float L = 0.f;
   for (int s = 0; s < splits; s++) { const float ms = p0[s * stride + E]; if (ms > -INFINITY) L += p0[s * stride + E + 1] * expf(ms - M); }
+  // lane s keeps split s's factor (at most 16 splits); splits that saw nothing have factor 0 and are not read
+  float w = 0.f;
+  if (lane < splits) { const float ms = p0[lane * stride + E]; w = ms > -INFINITY ? expf(ms - M) : 0.f; }
   for (int e = lane; e < E; e += 32) {
     float o = 0.f;
-    for (int s = 0; s < splits; s++) { const float ms = p0[s * stride + E]; if (ms > -INFINITY) o = fmaf(p0[s * stride + e], expf(ms - M), o); }
+    for (int s = 0; s < splits; s++) { const float ws = __shfl_sync(THA_FULL_MASK, w, s); if (ws > 0.f) o = fmaf(p0[s * stride + e], ws, o); }
     hyb_store(out + (size_t)idx * E + e, o / L);
   }
 }
@@ -1334,6 +1349,21 @@ extern "C" int tha_hyb_norm(void* stream, int dtype, void* out, const float* x, 
   else
     THA_CUDA_OK(launch(hyb_dyt_kernel<float>, dim3(n_rows), dim3(nt), 0, (cudaStream_t)stream, false, (float*)out, x, n->w, n->b, n->alpha, width, rows_idx));
   return THA_STATUS_SUCCESS;
+}
+
+extern "C" int tha_hyb_norm_pair(void* stream, int dtype, void* out1, void* out2, const float* x, const tha_norm_t* n1, const tha_norm_t* n2,
+                                 float eps, int n_rows, int width) {
+  if (n1->kind == THA_NORM_DYT && n2->kind == THA_NORM_DYT && n1->w && n2->w) {
+    if (n_rows < 1) return THA_STATUS_SUCCESS;
+    const int nt = pick_threads(width);
+    if (dtype == THA_DT_BF16)
+      THA_CUDA_OK(launch(hyb_dyt2_kernel<bf16>, dim3(n_rows), dim3(nt), 0, (cudaStream_t)stream, false, (bf16*)out1, (bf16*)out2, x, *n1, *n2, width));
+    else
+      THA_CUDA_OK(launch(hyb_dyt2_kernel<float>, dim3(n_rows), dim3(nt), 0, (cudaStream_t)stream, false, (float*)out1, (float*)out2, x, *n1, *n2, width));
+    return THA_STATUS_SUCCESS;
+  }
+  const int st = tha_hyb_norm(stream, dtype, out1, x, n1, eps, n_rows, width, nullptr);
+  return st != THA_STATUS_SUCCESS ? st : tha_hyb_norm(stream, dtype, out2, x, n2, eps, n_rows, width, nullptr);
 }
 
 extern "C" int tha_hyb_linear_heads(void* stream, int dtype, float* C, long long ldc, long long c_hs, const void* A, long long lda,

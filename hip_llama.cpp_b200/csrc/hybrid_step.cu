@@ -231,7 +231,9 @@ extern "C" int tha_hyb_step(void* stream, const tha_hyb_model_t* m, const tha_ro
   for (int li = 0; li < m->n_layers; li++) {
     const tha_hyb_layer_t& L = m->layers[li];
     const long long ldp = L.n_in;
-    HYB_OK(tha_hyb_norm(stream, dt, b.h, b.x, &L.norm1, m->eps, R, W, nullptr));
+    const bool two_norms = L.has_norm2 && L.has_ff != THA_FF_NONE;
+    if (two_norms) HYB_OK(tha_hyb_norm_pair(stream, dt, b.h, b.h2, b.x, &L.norm1, &L.norm2, m->eps, R, W));
+    else HYB_OK(tha_hyb_norm(stream, dt, b.h, b.x, &L.norm1, m->eps, R, W, nullptr));
     HYB_OK(tha_hyb_linear(stream, dt, b.proj, ldp, b.h, W, 0, nullptr, L.w_in, 0, R, L.n_in, W, nullptr, 0));
     const float* right = nullptr;
     if (L.mixer == THA_MIX_PARALLEL) {
@@ -289,8 +291,7 @@ extern "C" int tha_hyb_step(void* stream, const tha_hyb_model_t* m, const tha_ro
     const void* hf = b.h;
     const float* fproj = b.proj;
     long long ldf = ldp;
-    if (L.has_norm2 && L.has_ff != THA_FF_NONE) {
-      HYB_OK(tha_hyb_norm(stream, dt, b.h2, b.x, &L.norm2, m->eps, R, W, nullptr));
+    if (two_norms) {
       HYB_OK(tha_hyb_linear(stream, dt, b.proj2, L.n_in2, b.h2, W, 0, nullptr, L.w_in2, 0, R, L.n_in2, W, nullptr, 0));
       hf = b.h2; fproj = b.proj2; ldf = L.n_in2;
     }

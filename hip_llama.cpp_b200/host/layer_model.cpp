@@ -290,7 +290,7 @@ LayerModel* LayerModel::build(const LayerProgramSpec& spec, const SafeTensors& f
           state += (2ll * L.delta.kv_heads * L.delta.dim + (long long)L.delta.heads * L.delta.vdim) * (L.delta.taps - 1);
         } else if (L.mixer == THA_MIX_GLA) {
           L.gla.state_off = state;
-          state += (long long)L.gla.heads * L.gla.dim * L.gla.vdim;
+          state += (long long)L.gla.heads * L.gla.dim * ((L.gla.vdim + 7) / 8 * 8);   // value columns padded to eights
         } else if (L.mixer == THA_MIX_LATENT) {
           L.latent.cache_layer = m->n_cache_layers_++;
         }
@@ -391,7 +391,7 @@ LayerModel* LayerModel::build(const LayerProgramSpec& spec, const SafeTensors& f
         G.norm = vec(g.norm, g.vdim);
         G.w_o = mat(g.o, W, g.heads * g.vdim);
         G.state_off = state;
-        state += (long long)g.heads * g.dim * g.vdim;
+        state += (long long)g.heads * g.dim * ((g.vdim + 7) / 8 * 8);   // value columns padded to eights
       } else if (ls.mixer == THA_MIX_LATENT) {
         const LatentSpec& a = ls.latent;
         if (a.heads < 1 || a.dim < 1 || a.vdim < 1 || a.q_rank < 1 || a.kv_rank < 1 || a.rot_dim < 0)

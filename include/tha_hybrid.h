@@ -146,7 +146,8 @@ typedef struct {
 
 /* Gated linear attention.  Per head S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T (q_t / sqrt(dim)), with the decay
  * a = sigmoid(z)^(1/tau) per key channel, z = W_a2 (W_a1 h) + b_a2.  The read-out is divided by its root mean square per
- * head, weighted (norm, [vdim], shared by the heads) and gated by silu(W_g h).  State per head: S [dim, vdim]. */
+ * head, weighted (norm, [vdim], shared by the heads) and gated by silu(W_g h).  State per head: dim x vdim floats, laid out for the
+ * scan ([column pair][key channel][2], an odd last column padded): heads * dim * (vdim rounded up to even) floats. */
 typedef struct {
   int heads, dim, vdim, rank;
   float tau, eps;
@@ -263,6 +264,9 @@ int tha_hyb_rmsnorm(void* stream, int dtype, void* out, const float* x, const fl
 /* the norm `n` of rows of x (picked through rows_idx when not NULL); out is dtype-typed */
 int tha_hyb_norm(void* stream, int dtype, void* out, const float* x, const tha_norm_t* n, float eps, int n_rows, int width,
                  const int* rows_idx);
+/* two norms of the same rows (the two norms of a parallel block): one pass over x where the kinds allow it */
+int tha_hyb_norm_pair(void* stream, int dtype, void* out1, void* out2, const float* x, const tha_norm_t* n1, const tha_norm_t* n2,
+                      float eps, int n_rows, int width);
 /* C[m, 0:N] = A[row(m), 0:K] . W_g[0:N, 0:K]^T, fp32 out.  a_f32: A is fp32 (else dtype-typed).  gather: row(m) =
  * a_rows[m] (NULL: m).  Groups: rows group_off[g] .. group_off[g+1]-1 use the matrix W + g * w_group_stride elements
  * (group_off NULL: one group of M rows). */
