@@ -37,18 +37,21 @@ void BatchManager::destroy_state_slots() {
 }
 
 // ---- paged mode ---------------------------------------------------------------------------------
-bool BatchManager::create_pool(size_t n_blocks) {
+bool BatchManager::create_pool(size_t n_blocks, bool with_values) {
   destroy_pool();
   const size_t blk_floats = (size_t)n_layers * block_size * kv_dim;
   if (n_blocks < 1) return false;
   if (tha_malloc((void**)&pool_k_, n_blocks * blk_floats * sizeof(float)) != 0) { pool_k_ = nullptr; return false; }
-  if (tha_malloc((void**)&pool_v_, n_blocks * blk_floats * sizeof(float)) != 0) { tha_free(pool_k_); pool_k_ = pool_v_ = nullptr; return false; }
+  // models whose value rows lie inside their key rows keep ONE pool: pool_v() then names the K pool
+  if (!with_values) pool_v_ = pool_k_;
+  else if (tha_malloc((void**)&pool_v_, n_blocks * blk_floats * sizeof(float)) != 0) { tha_free(pool_k_); pool_k_ = pool_v_ = nullptr; return false; }
   if (tha_malloc((void**)&table_d_, (size_t)batch_size * nrow_blocks * sizeof(int)) != 0) {
-    tha_free(pool_k_); tha_free(pool_v_); pool_k_ = pool_v_ = nullptr; table_d_ = nullptr;
+    tha_free(pool_k_); if (pool_v_ != pool_k_) tha_free(pool_v_);
+    pool_k_ = pool_v_ = nullptr; table_d_ = nullptr;
     return false;
   }
   tha_memset(pool_k_, 0, n_blocks * blk_floats * sizeof(float));
-  tha_memset(pool_v_, 0, n_blocks * blk_floats * sizeof(float));
+  if (pool_v_ != pool_k_) tha_memset(pool_v_, 0, n_blocks * blk_floats * sizeof(float));
   tha_memset(table_d_, 0, (size_t)batch_size * nrow_blocks * sizeof(int));
   pool_blocks_ = n_blocks;
   num_physical_blocks = n_blocks;
@@ -70,7 +73,8 @@ void BatchManager::destroy_pool() {
   if (!pool_blocks_) return;
   tha_kv_pool_unregister(pool_k_);
   if (bound_ && bound_->key_cache == pool_k_) { bound_->key_cache = nullptr; bound_->value_cache = nullptr; }
-  tha_free(pool_k_); tha_free(pool_v_); tha_free(table_d_);
+  if (pool_v_ != pool_k_) tha_free(pool_v_);
+  tha_free(pool_k_); tha_free(table_d_);
   pool_k_ = pool_v_ = nullptr; table_d_ = nullptr;
   pool_blocks_ = 0;
   free_list_.clear();

@@ -317,6 +317,7 @@ LayerModel* LayerModel::build(const LayerProgramSpec& spec, const SafeTensors& f
           A.rot = rotary(a.rot);
         }
         A.cache_layer = m->n_cache_layers_++;
+        m->separate_values_ = true;
         m->kv_dim_ = std::max(m->kv_dim_, std::max(a.kv_heads * a.dim, a.kv_heads * a.vdim));
         A.o_q = in.add(a.q, (long long)a.heads * a.dim);
         A.o_k = in.add(a.k, (long long)a.kv_heads * a.dim);

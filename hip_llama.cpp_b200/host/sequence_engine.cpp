@@ -17,7 +17,7 @@ SequenceEngine::SequenceEngine(LayerModel* model, int max_tokens, int max_seqs)
       max_seqs_(max_seqs) {
   if (max_tokens < 1 || max_seqs < 1) { err_ = "max_tokens and max_seqs must be positive"; return; }
   const size_t blocks = bm_.blocks_for(round_up(max_tokens, 64));
-  if (!bm_.create_pool(blocks)) { err_ = std::string("cannot allocate the cache pool: ") + tha_last_error(); return; }
+  if (!bm_.create_pool(blocks, model->separate_values())) { err_ = std::string("cannot allocate the cache pool: ") + tha_last_error(); return; }
   if (!bm_.create_state_slots((size_t)model->state_floats())) { err_ = std::string("cannot allocate the state slots: ") + tha_last_error(); return; }
   if (tha_stream_create(&stream_) != 0) { err_ = tha_last_error(); return; }
   filled_.assign(max_seqs, 0);

@@ -72,7 +72,9 @@ class BatchManager {
   void dealloc_gpu_block(int seq_id);
 
   // ---- paged mode ------------------------------------------------------------------------------
-  bool create_pool(size_t n_blocks);              // allocate the pools and the device table (current device); false: no memory
+  // allocate the pools and the device table (current device); false: no memory.  with_values = false: one pool only
+  // (pool_v() == pool_k()), for models whose value rows are part of their key rows
+  bool create_pool(size_t n_blocks, bool with_values = true);
   void destroy_pool();
   void bind_paged(RunState* s_d);                 // point s_d->key_cache / value_cache at the pools (the state must not own slabs)
   bool paged() const { return pool_blocks_ > 0; }

@@ -149,6 +149,7 @@ class LayerModel {
   int max_positions() const { return spec_.pos_embed.empty() ? 0 : spec_.max_positions; }   // 0: no limit
   int n_cache_layers() const { return n_cache_layers_; }
   int kv_dim() const { return kv_dim_; }                    // widest K or V row (floats)
+  bool separate_values() const { return separate_values_; } // false: every cached layer's values lie inside its key rows
   long long state_floats() const { return state_floats_; }  // recurrent state of one sequence
   size_t weight_bytes() const { return weight_bytes_; }
 
@@ -162,6 +163,7 @@ class LayerModel {
   std::vector<RotarySpec> rot_specs_;
   std::vector<void*> owned_;
   int n_cache_layers_ = 0, kv_dim_ = 0;
+  bool separate_values_ = false;
   long long state_floats_ = 0;
   size_t weight_bytes_ = 0;
 };
