@@ -9,7 +9,7 @@
 //   * warp 16 of every CTA is a PRODUCER: it walks the CTA's static list of weight row-pairs for
 //     the whole step (its share of wq|wk|wv, wo, w1&w3, w2 of every layer, then of wcls) and
 //     streams them HBM -> shared memory with 1-D bulk async copies (cp.async.bulk, the TMA
-//     engine; SASS UBLKCP) into a ring of 10 x 16 KB slots, gated only by slot reuse
+//     engine) into a ring of 10 x 16 KB slots, gated only by slot reuse
 //     (mbarrier full/empty pairs) -- never by a grid barrier.  ~24 MB are in flight chip-wide.
 //   * warps 0-15 are CONSUMERS: per phase they wait for the grid barrier (activations of the
 //     previous phase are complete), stage the B activation rows in shared memory (RMSNorm
